@@ -137,6 +137,31 @@ class SigmoidAttentionSpec:
 
 
 @dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Causal grouped-query softmax attention without a rotation, whose positions enter through a bias on the distance:
+    score(i, j) = q_i . k_j * ``scale`` - r1_h * ln(1 + r2_h * (i - j)) with two learned numbers per query head
+    (``distance_bias``). With ``sink`` the softmax's denominator also holds exp(sink_h), a learned logit per head that has no
+    key and no value. Queries and keys have ``head_dim`` channels and are RMS-normed per head (``qk_norm_eps``; None: no
+    norm; one gain for all query heads, one for all key heads); values have ``value_dim`` channels. ``value_mix``:
+    "none"; "source": this layer's values are kept for the step, for later layers to mix in; "mixed": the values become
+    (1 - lambda) v + lambda v_source (lambda a learned scalar, v_source the source layer's values of the same token) before
+    they are cached. ``output_gate``: head h's output is multiplied by sigmoid(w_gate_h . x), one number per head and
+    token, from the same input as the projections. ``window`` as in ``GqaAttentionSpec``."""
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: Optional[int] = None
+    qk_norm_eps: Optional[float] = None
+    distance_bias: bool = True
+    sink: bool = True
+    value_mix: str = "none"
+    output_gate: bool = True
+    kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
 class MinGruSpec:
     """minGRU: per channel S_t = (1 - z_t) S_(t-1) + z_t c_t with the gate z_t = sigmoid(W_z h + b_z) and the candidate c_t
     from u = W_x h + b_x (u + 1/2 where u >= 0, sigmoid(u) elsewhere), both functions of the current token alone; the
@@ -162,6 +187,15 @@ class RoutedExpertsSpec:
     correction: bool = True
     shared_size: int = 0
     shared_gate: bool = True
+    #: "sigmoid": as above. "softmax_chosen": the choice is made by the logits themselves (plus ``router_bias``, a stored
+    #: number per expert that is part of the logit) and the weights are the softmax over the chosen logits alone
+    scoring: str = "sigmoid"
+    router_bias: bool = False
+    #: "relu2": W_down relu(W_up h)^2. "clamped_glu": the expert has a gate and an up matrix and computes
+    #: W_down (g * sigmoid(``glu_slope`` g) * (u + 1)) with g = min(W_gate h, ``limit``), u = clamp(W_up h, -limit, limit)
+    activation: str = "relu2"
+    limit: float = 0.0
+    glu_slope: float = 1.702
     kind: str = "routed_experts"
 
 
@@ -170,6 +204,18 @@ class SquaredReluSpec:
     """Dense feed-forward without a gate: down(relu(up(x))^2)."""
     intermediate_size: int
     kind: str = "relu2"
+
+
+@dataclass(frozen=True)
+class ClampedGluSpec:
+    """Dense gated feed-forward with clamped branches and biases: g = min(W_gate x + b_gate, ``limit``),
+    u = clamp(W_up x + b_up, -limit, limit), output W_down (g * sigmoid(``slope`` g) * (u + 1)) + b_down. ``bias`` False
+    leaves the three biases out."""
+    intermediate_size: int
+    limit: float
+    slope: float = 1.702
+    bias: bool = True
+    kind: str = "clamped_glu"
 
 
 @dataclass(frozen=True)
@@ -224,6 +270,8 @@ class LayerSpec:
     #: x += post(ffn(norm(x))); there ``ffn`` may be None (a layer without a feed-forward)
     mixer_post_norm: Any = None
     ffn_post_norm: Any = None
+    #: "branch_norm" norms each branch on the way out only: x += post(mixer(x)), x += post(ffn(x)); the branches read the
+    #: residual itself (rounded to the activation dtype); ``mixer_norm`` and ``ffn_norm`` are None, ``ffn`` may be None
     #: "hyper_connections": the residual is ``streams`` rows per token; each branch reads a learned mix of them through
     #: its norm and its output comes back into all of them through a learned matrix (``ModelConfig.residual_streams`` says
     #: the same number for the whole model); ``ffn`` may be None

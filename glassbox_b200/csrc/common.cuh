@@ -43,6 +43,12 @@ template <> __device__ __forceinline__ __nv_bfloat16 gb_from_float<__nv_bfloat16
     return __float2bfloat16_rn(v);
 }
 
+// The clamped gated unit: g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+__device__ __forceinline__ float gb_clamped_unit(float gate, float up, float limit, float slope) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -6,6 +6,11 @@
 //                    member); only experts of the `keep` best runs can be chosen, the others count as minus infinity. The
 //                    `top` largest are taken (among equals the lowest index), each with the weight s * route_scale, not
 //                    renormalised. Also the gate of a shared expert, sigmoid(w_gate . h), one number per row.
+//                    With softmax_chosen the scores are the logits themselves (plus a stored bias per expert), the `top`
+//                    largest are taken and their weights are the softmax over the chosen logits alone.
+//                    An expert is either W_down relu(W_up h)^2 or (UNIT) W_down unit(W_gate h, W_up h) with the clamped
+//                    gated unit g * sigmoid(slope g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); its
+//                    up matrix then holds gate row f and up row f as rows 2f and 2f + 1.
 //   moe_expert_rows  one block per (row, chosen expert): act = relu(W_up[e] h)^2 in shared memory, then W_down[e] act,
 //                    written as float32 per (row, choice). Reads the two matrices of one expert once per block: the
 //                    form for few rows (decoding), and the float32 path's form for any number.
@@ -79,7 +84,8 @@ __device__ __forceinline__ int moe_warp_argmax(const float* v, int count, int la
 
 // The choice for one row, by one warp: `score`, `choice` (score + correction), `run_score` and `kept` are the row's arrays.
 __device__ __forceinline__ void moe_choose(const float* score, float* choice, float* run_score, unsigned char* kept, int E, int top,
-                                           int groups, int keep, float route_scale, int* choice_out, float* weight_out, int lane) {
+                                           int groups, int keep, float route_scale, int* choice_out, float* weight_out, int lane,
+                                           bool softmax_chosen = false) {
     if (groups > 1 && keep < groups) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
@@ -112,6 +118,18 @@ __device__ __forceinline__ void moe_choose(const float* score, float* choice, fl
         }
         __syncwarp();
     }
+    if (softmax_chosen && lane == 0) {
+        // weight_out holds the chosen logits, the largest first: softmax over them alone
+        const float m = weight_out[0];
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float w = choice_out[k] >= 0 ? expf(weight_out[k] - m) : 0.f;
+            weight_out[k] = w;
+            sum += w;
+        }
+        const float inv = 1.0f / sum;
+        for (int k = 0; k < top; ++k) weight_out[k] *= inv;
+    }
 }
 
 // RB rows per block: a warp per expert (and one for the shared gate) reads its row of the router matrix once and dots it
@@ -121,7 +139,8 @@ template <typename T, int RB, int EMAX>
 __global__ void __launch_bounds__(RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THREADS) moe_route_kernel(
     const T* __restrict__ h, int d, const float* __restrict__ w_router, const float* __restrict__ correction,
     const float* __restrict__ w_gate, const int* __restrict__ positions, int n, int E, int top, int groups, int keep,
-    float route_scale, int* __restrict__ choice_out, float* __restrict__ weight_out, float* __restrict__ gate_out) {
+    float route_scale, int* __restrict__ choice_out, float* __restrict__ weight_out, float* __restrict__ gate_out,
+    const float* __restrict__ router_bias, int softmax_chosen) {
     extern __shared__ __align__(16) float moe_smem[];
     float* hx = moe_smem;                       // RB rows of d numbers (rows start 16-byte aligned: ldh is a multiple of 4)
     const int ldh = (d + 3) & ~3;
@@ -171,7 +190,9 @@ __global__ void __launch_bounds__(RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THR
             const int row = row0 + r;
             if (lane == 0 && row < n && positions[row] >= 0) {
                 const float sg = moe_sigmoid(z);
-                if (e < E) {
+                if (e < E && softmax_chosen) {
+                    score[r][e] = choice[r][e] = z + (router_bias ? router_bias[e] : 0.f);
+                } else if (e < E) {
                     score[r][e] = sg;
                     choice[r][e] = sg + (correction ? correction[e] : 0.f);
                 } else {
@@ -184,27 +205,29 @@ __global__ void __launch_bounds__(RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THR
     for (int r = warp; r < RB; r += warps) {
         const int row = row0 + r;
         if (row < n && positions[row] >= 0)
-            moe_choose(score[r], choice[r], run_score[r], kept[r], E, top, groups, keep, route_scale, choice_out + (size_t)row * top,
-                       weight_out + (size_t)row * top, lane);
+            moe_choose(score[r], choice[r], run_score[r], kept[r], E, top, groups, keep, softmax_chosen ? 1.0f : route_scale,
+                       choice_out + (size_t)row * top, weight_out + (size_t)row * top, lane, softmax_chosen != 0);
     }
 }
 
 template <typename T, int RB, int EMAX>
 static void moe_route_launch(const void* h, int d, const float* w_router, const float* correction, const float* w_gate,
                              const int* positions, int n, int E, int top, int groups, int keep, float route_scale, int* choice_out,
-                             float* weight_out, float* gate_out, cudaStream_t stream) {
+                             float* weight_out, float* gate_out, const float* router_bias, int softmax_chosen, cudaStream_t stream) {
     const size_t smem = (size_t)RB * ((d + 3) & ~3) * 4;
     int warps = E + (w_gate ? 1 : 0);
     const int most = (RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THREADS) / 32, least = RB > 4 ? RB : 4;
     warps = warps < least ? least : (warps > most ? most : warps);
     if (smem > 32 * 1024) cudaFuncSetAttribute(moe_route_kernel<T, RB, EMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<T, RB, EMAX>, dim3(gb_ceil_div(n, RB)), dim3(32 * warps), smem, stream, (const T*)h, d,
-              w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out, weight_out, gate_out);
+              w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out, weight_out, gate_out, router_bias,
+              softmax_chosen);
 }
 
 GB_EXPORT int gb_moe_route(const void* h, int h_dtype, int d, const float* w_router, const float* correction, const float* w_gate,
                            const int* positions, int n, int E, int top, int groups, int keep, float route_scale, int* choice_out,
-                           float* weight_out, float* gate_out, cudaStream_t stream) {
+                           float* weight_out, float* gate_out, const float* router_bias, int softmax_chosen, cudaStream_t stream) {
+    GB_REQUIRE(!softmax_chosen || (groups == 1 && correction == nullptr), "gb_moe_route: softmax over the chosen logits goes with neither groups nor a correction");
     GB_REQUIRE(n >= 0 && d > 0 && E > 0 && E <= MOE_MAX_EXPERTS && top > 0 && top <= E, "gb_moe_route: bad sizes (experts %d, top %d)", E,
                top);
     GB_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups, "gb_moe_route: %d experts in %d groups, %d kept", E, groups,
@@ -218,10 +241,10 @@ GB_EXPORT int gb_moe_route(const void* h, int h_dtype, int d, const float* w_rou
 #define MOE_ROUTE_GO(T)                                                                                                              \
     if (many)                                                                                                                        \
         moe_route_launch<T, 8, 128>(h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out,  \
-                                    weight_out, gate_out, stream);                                                                   \
+                                    weight_out, gate_out, router_bias, softmax_chosen, stream);                                      \
     else                                                                                                                             \
         moe_route_launch<T, 1, MOE_MAX_EXPERTS>(h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale,  \
-                                                choice_out, weight_out, gate_out, stream);
+                                                choice_out, weight_out, gate_out, router_bias, softmax_chosen, stream);
     if (h_dtype == GB_F32) { MOE_ROUTE_GO(float) } else { MOE_ROUTE_GO(__nv_bfloat16) }
 #undef MOE_ROUTE_GO
     return gb_check_launch("gb_moe_route");
@@ -328,7 +351,8 @@ GB_EXPORT int gb_moe_combine(const float* pair, const float* weight, int top, co
 template <typename T, bool UP>
 __global__ void __launch_bounds__(256) moe_half_rows_kernel(const void* __restrict__ in_, long long ld_in, const T* __restrict__ w, int N,
                                                             int K, const int* __restrict__ choice, const int* __restrict__ positions,
-                                                            int n, int E, int top, float* __restrict__ out, long long ld_out) {
+                                                            int n, int E, int top, float* __restrict__ out, long long ld_out,
+                                                            int unit, float limit, float slope) {
     extern __shared__ __align__(16) float moe_smem[];
     float* x = moe_smem;       // K numbers: the row h (UP) or the pair's activations (DOWN)
     const int pair = blockIdx.x, row = pair / top;
@@ -337,7 +361,8 @@ __global__ void __launch_bounds__(256) moe_half_rows_kernel(const void* __restri
     gb_pdl_launch_dependents();
     gb_pdl_wait();                // (the choice is the router kernel's output: nothing of it may be read before this)
     const int e = (row < n && positions[row] >= 0) ? choice[pair] : -2;
-    const T* wrow = (e >= 0 && e < E && c < N) ? w + ((size_t)e * N + c) * K : nullptr;
+    // (with the gated unit an expert has 2N rows: output c reads its gate row 2c and its up row 2c + 1)
+    const T* wrow = (e >= 0 && e < E && c < N) ? w + ((size_t)e * N + c) * K * (UP && unit ? 2 : 1) : nullptr;
     if (e == -2) return;
     if (e < 0 || e >= E) {
         if (c < N && lane == 0) out[(size_t)pair * ld_out + c] = 0.f;
@@ -353,7 +378,9 @@ __global__ void __launch_bounds__(256) moe_half_rows_kernel(const void* __restri
     __syncthreads();
     if (wrow == nullptr) return;
     float v = moe_warp_dot<T>(wrow, x, K, lane);
-    if (UP) {
+    if (UP && unit) {
+        v = gb_clamped_unit(v, moe_warp_dot<T>(wrow + K, x, K, lane), limit, slope);
+    } else if (UP) {
         v = fmaxf(v, 0.f);
         v *= v;
     }
@@ -362,31 +389,33 @@ __global__ void __launch_bounds__(256) moe_half_rows_kernel(const void* __restri
 
 template <typename T>
 static int moe_half_rows_launch(const void* h, int d, const T* w_up, const T* w_down, int ff, const int* choice, const int* positions,
-                                int n, int E, int top, float* act, float* pair, cudaStream_t stream) {
+                                int n, int E, int top, float* act, float* pair, int unit, float limit, float slope, cudaStream_t stream) {
     const size_t smem_up = (size_t)d * 4, smem_down = (size_t)ff * 4;
     if (smem_up > 32 * 1024)
         cudaFuncSetAttribute(moe_half_rows_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
     if (smem_down > 32 * 1024)
         cudaFuncSetAttribute(moe_half_rows_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     gb_launch(GB_PDL_GEMM, moe_half_rows_kernel<T, true>, dim3(n * top, gb_ceil_div(ff, 8)), dim3(256), smem_up, stream, h, (long long)d,
-              w_up, ff, d, choice, positions, n, E, top, act, (long long)ff);
+              w_up, ff, d, choice, positions, n, E, top, act, (long long)ff, unit, limit, slope);
     int rc = gb_check_launch("gb_moe_expert_halves (up)");
     if (rc) return rc;
     gb_launch(GB_PDL_GEMM, moe_half_rows_kernel<T, false>, dim3(n * top, gb_ceil_div(d, 8)), dim3(256), smem_down, stream,
-              (const void*)act, (long long)ff, w_down, d, ff, choice, positions, n, E, top, pair, (long long)d);
+              (const void*)act, (long long)ff, w_down, d, ff, choice, positions, n, E, top, pair, (long long)d, 0, 0.f, 0.f);
     return gb_check_launch("gb_moe_expert_halves (down)");
 }
 
 GB_EXPORT int gb_moe_expert_halves(const void* h, int dtype, int d, const void* w_up, const void* w_down, int ff, const int* choice,
-                                   const int* positions, int n, int E, int top, float* act, float* pair, cudaStream_t stream) {
+                                   const int* positions, int n, int E, int top, float* act, float* pair, int unit, float limit, float slope,
+                                   cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && d > 0 && ff > 0 && E > 0 && top > 0, "gb_moe_expert_halves: bad sizes");
     GB_REQUIRE((size_t)d * 4 <= 200 * 1024 && (size_t)ff * 4 <= 200 * 1024, "gb_moe_expert_halves: rows of %d / %d numbers do not fit", d, ff);
     if (n == 0) return 0;
     if (dtype == GB_F32)
-        return moe_half_rows_launch<float>(h, d, (const float*)w_up, (const float*)w_down, ff, choice, positions, n, E, top, act, pair, stream);
+        return moe_half_rows_launch<float>(h, d, (const float*)w_up, (const float*)w_down, ff, choice, positions, n, E, top, act, pair, unit,
+                                           limit, slope, stream);
     if (dtype == GB_BF16)
         return moe_half_rows_launch<__nv_bfloat16>(h, d, (const __nv_bfloat16*)w_up, (const __nv_bfloat16*)w_down, ff, choice, positions,
-                                                   n, E, top, act, pair, stream);
+                                                   n, E, top, act, pair, unit, limit, slope, stream);
     GB_REQUIRE(false, "gb_moe_expert_halves: unsupported dtype %d", dtype);
 }
 
@@ -449,7 +478,8 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_gemm_kernel(const __nv
                                                                const __nv_bfloat16* __restrict__ W, int N, int K,
                                                                const int* __restrict__ sorted, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_start, int E, int top,
-                                                               void* __restrict__ C, long long ldc) {
+                                                               void* __restrict__ C, long long ldc, int unit, float limit,
+                                                               float slope) {
     extern __shared__ __align__(16) unsigned char mg_smem[];
     __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(mg_smem);                 // [stages][BM][LD]
     __nv_bfloat16* sb = sa + MG_STAGES * MG_BM * MG_LD;                            // [stages][BN][LD]
@@ -552,7 +582,10 @@ __global__ void __launch_bounds__(MG_THREADS) moe_grouped_gemm_kernel(const __nv
             for (int j = 0; j < 4; ++j) {
                 const int col = n0 + wn + j * 8 + (lane & 3) * 2;
                 float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
-                if (UP) {
+                if (UP && unit) {
+                    // neighbouring outputs are the gate sum and the up sum of one unit: N / 2 units per row
+                    if (col + 1 < N) ((__nv_bfloat16*)C)[(size_t)out_row * ldc + (col >> 1)] = __float2bfloat16_rn(gb_clamped_unit(v0, v1, limit, slope));
+                } else if (UP) {
                     v0 = fmaxf(v0, 0.f); v0 *= v0;
                     v1 = fmaxf(v1, 0.f); v1 *= v1;
                     __nv_bfloat16* o = (__nv_bfloat16*)C + (size_t)out_row * ldc + col;
@@ -582,7 +615,9 @@ GB_EXPORT int gb_moe_sort(const int* choice, const int* positions, int n, int E,
 GB_EXPORT int gb_moe_grouped_supported(int d, int ff) { return d % 8 == 0 && ff % 8 == 0 ? 1 : 0; }
 
 GB_EXPORT int gb_moe_grouped_gemm(const void* a, long long lda, const void* w, int N, int K, const int* sorted, const int* offsets,
-                                  const int* tile_start, int E, int top, int pairs, void* c, long long ldc, int up, cudaStream_t stream) {
+                                  const int* tile_start, int E, int top, int pairs, void* c, long long ldc, int up, int unit, float limit,
+                                  float slope, cudaStream_t stream) {
+    GB_REQUIRE(!unit || (up && N % 2 == 0), "gb_moe_grouped_gemm: the gated unit belongs to the up half and needs pairs of rows");
     GB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && pairs >= 0, "gb_moe_grouped_gemm: rows must be whole 16-byte pieces (K=%d)", K);
     GB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gb_moe_grouped_gemm: operands must be 16-byte aligned");
     if (pairs == 0) return 0;
@@ -591,9 +626,9 @@ GB_EXPORT int gb_moe_grouped_gemm(const void* a, long long lda, const void* w, i
     cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM);
     if (up)
         gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(MG_THREADS), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
-                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
+                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc, unit, limit, slope);
     else
         gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(MG_THREADS), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
-                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
+                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc, 0, 0.f, 0.f);
     return gb_check_launch("gb_moe_grouped_gemm");
 }

@@ -1,6 +1,10 @@
 // Small row-wise and element-wise kernels for layers that norm a branch before it joins the residual stream, for
 // activations other than SwiGLU, and for a scaled head:
-//   rmsnorm_add   x[r, :] += gain * y[r, :] / sqrt(mean(y[r, :]^2) + eps)   (float32 throughout)
+//   rmsnorm_add   x[r, :] += gain * y[r, :] / sqrt(mean(y[r, :]^2) + eps)   (float32 throughout); optionally y + bias in the
+//                 place of y, and a copy of the new x[r, :] in the activation dtype
+//   cast_rows     out[r, :] = x[rows[r], :] in the activation dtype
+//   add_bias      y[r, :] += bias
+//   clamped_glu   act[r, f] = g * sigmoid(slope * g) * (u + 1), g = min(gate + b, limit), u = clamp(up + b, -limit, limit)
 //   relu2         out = max(in, 0)^2
 //   scale         t *= s
 //   gated_head_norm  out[r, h, :] = w * o[r, h, :] / sqrt(mean_v(o[r, h, :]^2) + eps) * sigmoid(gate[r, h, :])
@@ -9,10 +13,11 @@
 // ----------------------------------------------------------------------------------------------
 // A branch's output y (float32) is normalised and added into the residual x (float32). One block per row.
 // ----------------------------------------------------------------------------------------------
-template <int THREADS>
+template <int THREADS, typename T>
 __global__ void __launch_bounds__(THREADS) rmsnorm_add_kernel(const float* __restrict__ y, long long ldy,
                                                               const float* __restrict__ gain, float* __restrict__ x,
-                                                              long long ldx, int n, int d, float eps) {
+                                                              long long ldx, int n, int d, float eps,
+                                                              const float* __restrict__ bias, T* __restrict__ copy) {
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int r = blockIdx.x;
@@ -23,7 +28,8 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_add_kernel(const float* __res
     __shared__ float total;
     constexpr int VMAX = 4;
     const bool quick = d % 4 == 0 && d <= THREADS * 4 * VMAX && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0 &&
-                       ((uintptr_t)gain & 15) == 0;
+                       ((uintptr_t)gain & 15) == 0 && ((uintptr_t)bias & 15) == 0;
+    T* cp = copy ? copy + (size_t)r * d : nullptr;
     float4 v[VMAX], o[VMAX];
     float ss = 0.f;
     if (quick) {
@@ -32,6 +38,10 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_add_kernel(const float* __res
             const int j = (i * THREADS + threadIdx.x) * 4;
             v[i] = j < d ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
             o[i] = j < d ? *reinterpret_cast<const float4*>(dst + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (bias != nullptr && j < d) {
+                const float4 b = *reinterpret_cast<const float4*>(bias + j);
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
         }
 #pragma unroll
         for (int i = 0; i < VMAX; ++i) {
@@ -40,7 +50,7 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_add_kernel(const float* __res
         }
     } else {
         for (int j = threadIdx.x; j < d; j += THREADS) {
-            const float t = src[j];
+            const float t = src[j] + (bias ? bias[j] : 0.f);
             ss = fmaf(t, t, ss);
         }
     }
@@ -67,19 +77,128 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_add_kernel(const float* __res
                 w.z = o[i].z + g.z * (v[i].z * s);
                 w.w = o[i].w + g.w * (v[i].w * s);
                 *reinterpret_cast<float4*>(dst + j) = w;
+                if (cp != nullptr) {
+                    cp[j] = gb_from_float<T>(w.x); cp[j + 1] = gb_from_float<T>(w.y);
+                    cp[j + 2] = gb_from_float<T>(w.z); cp[j + 3] = gb_from_float<T>(w.w);
+                }
             }
         }
     } else {
-        for (int j = threadIdx.x; j < d; j += THREADS) dst[j] += gain[j] * (src[j] * s);
+        for (int j = threadIdx.x; j < d; j += THREADS) {
+            const float w = dst[j] + gain[j] * ((src[j] + (bias ? bias[j] : 0.f)) * s);
+            dst[j] = w;
+            if (cp != nullptr) cp[j] = gb_from_float<T>(w);
+        }
     }
 }
 
+// bias (optional, float32 [d]) is added to y first; copy (optional, [n, d] of dtype copy_dtype) receives the new x
 GB_EXPORT int gb_rmsnorm_add(const float* y, long long ldy, const float* gain, float* x, long long ldx, int n, int d,
-                             float eps, cudaStream_t stream) {
+                             float eps, const float* bias, void* copy, int copy_dtype, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && d > 0, "gb_rmsnorm_add: bad sizes n=%d d=%d", n, d);
+    GB_REQUIRE(copy == nullptr || copy_dtype == GB_F32 || copy_dtype == GB_BF16, "gb_rmsnorm_add: unsupported dtype %d", copy_dtype);
     if (n == 0) return 0;
-    gb_launch(GB_PDL_ELEMENTWISE, rmsnorm_add_kernel<128>, dim3(n), dim3(128), 0, stream, y, ldy, gain, x, ldx, n, d, eps);
+    if (copy != nullptr && copy_dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, rmsnorm_add_kernel<128, __nv_bfloat16>, dim3(n), dim3(128), 0, stream, y, ldy, gain, x, ldx, n, d,
+                  eps, bias, (__nv_bfloat16*)copy);
+    else
+        gb_launch(GB_PDL_ELEMENTWISE, rmsnorm_add_kernel<128, float>, dim3(n), dim3(128), 0, stream, y, ldy, gain, x, ldx, n, d, eps,
+                  bias, (float*)copy);
     return gb_check_launch("gb_rmsnorm_add");
+}
+
+// ----------------------------------------------------------------------------------------------
+// out[r, :] = x[rows ? rows[r] : r, :], float32 -> the activation dtype (a branch that reads the residual as it is).
+// ----------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, long long ldx, const int* __restrict__ rows, T* __restrict__ out, int n,
+                                 int d) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long total = (long long)n * d;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / d), j = (int)(idx % d);
+        const int src = rows ? rows[r] : r;
+        out[idx] = gb_from_float<T>(src >= 0 ? x[(size_t)src * ldx + j] : 0.f);
+    }
+}
+
+GB_EXPORT int gb_cast_rows(const float* x, long long ldx, const int* rows, void* out, int dtype, int n, int d, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && d > 0, "gb_cast_rows: bad sizes n=%d d=%d", n, d);
+    if (n == 0) return 0;
+    long long total = (long long)n * d;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == GB_F32)
+        gb_launch(GB_PDL_ELEMENTWISE, cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, ldx, rows, (float*)out, n, d);
+    else if (dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, ldx, rows,
+                  (__nv_bfloat16*)out, n, d);
+    else
+        GB_REQUIRE(false, "gb_cast_rows: unsupported dtype %d", dtype);
+    return gb_check_launch("gb_cast_rows");
+}
+
+// ----------------------------------------------------------------------------------------------
+// y[r, :] += bias (float32): a product's bias where no later kernel takes it along.
+// ----------------------------------------------------------------------------------------------
+__global__ void add_bias_kernel(float* __restrict__ y, long long ldy, const float* __restrict__ bias, int n, int d) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long total = (long long)n * d;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / d), j = (int)(idx % d);
+        y[(size_t)r * ldy + j] += bias[j];
+    }
+}
+
+GB_EXPORT int gb_add_bias(float* y, long long ldy, const float* bias, int n, int d, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && d > 0, "gb_add_bias: bad sizes n=%d d=%d", n, d);
+    if (n == 0) return 0;
+    long long total = (long long)n * d;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gb_launch(GB_PDL_ELEMENTWISE, add_bias_kernel, dim3(blocks), dim3(256), 0, stream, y, ldy, bias, n, d);
+    return gb_check_launch("gb_add_bias");
+}
+
+// ----------------------------------------------------------------------------------------------
+// The clamped gated unit, from the sums of the stacked gate | up product (row r: ff gate sums, then ff up sums):
+// g = min(gate + b_gate, limit), u = clamp(up + b_up, -limit, limit), act = g * sigmoid(slope * g) * (u + 1), in float32.
+// ----------------------------------------------------------------------------------------------
+template <typename TI, typename T>
+__global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, long long ld, const float* __restrict__ bias, float limit,
+                                   float slope, T* __restrict__ act, int n, int ff) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long total = (long long)n * ff;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / ff), f = (int)(idx % ff);
+        const TI* row = gate_up + (size_t)r * ld;
+        act[idx] = gb_from_float<T>(gb_clamped_unit(gb_to_float(row[f]) + (bias ? bias[f] : 0.f),
+                                                   gb_to_float(row[ff + f]) + (bias ? bias[ff + f] : 0.f), limit, slope));
+    }
+}
+
+GB_EXPORT int gb_clamped_glu(const void* gate_up, int in_dtype, long long ld, const float* bias, float limit, float slope, void* act,
+                             int dtype, int n, int ff, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && ff > 0 && limit > 0.f, "gb_clamped_glu: bad sizes n=%d ff=%d limit=%g", n, ff, (double)limit);
+    if (n == 0) return 0;
+    long long total = (long long)n * ff;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (in_dtype == GB_F32 && dtype == GB_F32)
+        gb_launch(GB_PDL_ELEMENTWISE, clamped_glu_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, ld,
+                  bias, limit, slope, (float*)act, n, ff);
+    else if (in_dtype == GB_F32 && dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, clamped_glu_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up,
+                  ld, bias, limit, slope, (__nv_bfloat16*)act, n, ff);
+    else if (in_dtype == GB_BF16 && dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, clamped_glu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                  (const __nv_bfloat16*)gate_up, ld, bias, limit, slope, (__nv_bfloat16*)act, n, ff);
+    else
+        GB_REQUIRE(false, "gb_clamped_glu: unsupported dtypes %d -> %d", in_dtype, dtype);
+    return gb_check_launch("gb_clamped_glu");
 }
 
 // ----------------------------------------------------------------------------------------------

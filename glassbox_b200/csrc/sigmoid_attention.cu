@@ -6,12 +6,14 @@
 //   qk_norm_rope_write   per row: RMS norm of every query and key head over dim (one gain for all query heads, one for
 //                        all key heads, eps inside the root), rotation of the first `rot` channels in neighbouring pairs
 //                        (2i, 2i+1) by the angle float32(position) * inv_freq[i], q to the query buffer, k and v into the
-//                        cache at the row's slot. Input: the float32 sums of the stacked projection q | k | v.
+//                        cache at the row's slot. Input: the float32 sums of the stacked projection q | k | v. Optionally
+//                        the values are mixed on the way: values_in given, v <- (1 - lambda) v + lambda values_in[row]
+//                        (lambda one float32 number on the device); values_out given, it receives the row's (mixed) v.
 //   sigmoid_attention_rows  one warp per (row, head), any row (prompt portion or single token), both dtypes: 32 keys at a
 //                        time from the first visible one, a lane per key for the scores, a lane per channel for the sum.
 #include "common.cuh"
+#include "paged_rows.cuh"
 
-constexpr int SA_MAX_DIM = 256;
 constexpr int SA_WARPS = 4;
 
 template <typename T>
@@ -19,7 +21,8 @@ __global__ void __launch_bounds__(512) qk_norm_rope_write_kernel(
     const float* __restrict__ qkv, long long ld, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ q_out,
     T* __restrict__ kcache, T* __restrict__ vcache, int n, int H, int G, int D, int V, int rot, float eps, int page_size,
-    long long num_slots, int write_kv, int* __restrict__ status) {
+    long long num_slots, int write_kv, int* __restrict__ status, float* __restrict__ values_out, const float* __restrict__ values_in,
+    long long ld_values, const float* __restrict__ value_mix) {
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int row = blockIdx.x;
@@ -69,11 +72,15 @@ __global__ void __launch_bounds__(512) qk_norm_rope_write_kernel(
         }
         if ((D & 1) && lane == 0) dst[D - 1] = gb_from_float<T>(x[D - 1] * r * (gain ? gain[D - 1] : 1.f));
     }
-    if (store) {
+    if (store || values_out != nullptr) {
         const float* v = src + (size_t)(H + G) * D;
+        const float lam = values_in != nullptr ? *value_mix : 0.f;
         for (int idx = threadIdx.x; idx < G * V; idx += blockDim.x) {
             const int g = idx / V, i = idx % V;
-            vcache[((page * G + g) * page_size + off) * V + i] = gb_from_float<T>(v[idx]);
+            float val = v[idx];
+            if (values_in != nullptr) val = (1.0f - lam) * val + lam * values_in[(size_t)row * ld_values + idx];
+            if (values_out != nullptr) values_out[(size_t)row * ld_values + idx] = val;
+            if (store) vcache[((page * G + g) * page_size + off) * V + i] = gb_from_float<T>(val);
         }
     }
 }
@@ -81,8 +88,11 @@ __global__ void __launch_bounds__(512) qk_norm_rope_write_kernel(
 GB_EXPORT int gb_qk_norm_rope_write(const float* qkv, long long ld, const float* q_gain, const float* k_gain, const float* inv_freq,
                                     const int* positions, const int* slots, void* q_out, void* kcache, void* vcache, int dtype, int n,
                                     int H, int G, int D, int V, int rot, float eps, int page_size, long long num_slots, int write_kv,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, float* values_out, const float* values_in, long long ld_values,
+                                    const float* value_mix, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && H > 0 && G > 0 && D > 0 && V > 0, "gb_qk_norm_rope_write: bad sizes");
+    GB_REQUIRE(values_in == nullptr || value_mix != nullptr, "gb_qk_norm_rope_write: values to mix in need their weight");
+    GB_REQUIRE((values_in == nullptr && values_out == nullptr) || ld_values >= (long long)G * V, "gb_qk_norm_rope_write: rows of values are too short");
     GB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D, "gb_qk_norm_rope_write: %d rotated channels of %d", rot, D);
     GB_REQUIRE(rot == 0 || inv_freq != nullptr, "gb_qk_norm_rope_write: a rotation needs its frequencies");
     if (n == 0) return 0;
@@ -90,54 +100,14 @@ GB_EXPORT int gb_qk_norm_rope_write(const float* qkv, long long ld, const float*
     if (dtype == GB_F32)
         gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<float>, dim3(n), block, 0, stream, qkv, ld, q_gain, k_gain, inv_freq,
                   positions, slots, (float*)q_out, (float*)kcache, (float*)vcache, n, H, G, D, V, rot, eps, page_size, num_slots,
-                  write_kv, status);
+                  write_kv, status, values_out, values_in, ld_values, value_mix);
     else if (dtype == GB_BF16)
         gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(n), block, 0, stream, qkv, ld, q_gain, k_gain,
                   inv_freq, positions, slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n, H, G, D, V,
-                  rot, eps, page_size, num_slots, write_kv, status);
+                  rot, eps, page_size, num_slots, write_kv, status, values_out, values_in, ld_values, value_mix);
     else
         GB_REQUIRE(false, "gb_qk_norm_rope_write: unsupported dtype %d", dtype);
     return gb_check_launch("gb_qk_norm_rope_write");
-}
-
-// q . k over D channels; q in shared memory as float32, k a row of the cache.
-template <typename T>
-__device__ __forceinline__ float sa_dot(const float* __restrict__ q, const T* __restrict__ k, int D);
-
-template <>
-__device__ __forceinline__ float sa_dot<float>(const float* __restrict__ q, const float* __restrict__ k, int D) {
-    float d = 0.f;
-    if (D % 4 == 0 && ((uintptr_t)k & 15) == 0) {
-#pragma unroll 8
-        for (int i = 0; i < D; i += 4) {
-            const float4 kv = *reinterpret_cast<const float4*>(k + i);
-            d = fmaf(q[i], kv.x, d); d = fmaf(q[i + 1], kv.y, d); d = fmaf(q[i + 2], kv.z, d); d = fmaf(q[i + 3], kv.w, d);
-        }
-    } else {
-        for (int i = 0; i < D; ++i) d = fmaf(q[i], k[i], d);
-    }
-    return d;
-}
-
-template <>
-__device__ __forceinline__ float sa_dot<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int D) {
-    float d = 0.f;
-    if (D % 8 == 0 && ((uintptr_t)k & 15) == 0) {
-#pragma unroll 8
-        for (int i = 0; i < D; i += 8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float2 f = __bfloat1622float2(p[t]);
-                d = fmaf(q[i + 2 * t], f.x, d);
-                d = fmaf(q[i + 2 * t + 1], f.y, d);
-            }
-        }
-    } else {
-        for (int i = 0; i < D; ++i) d = fmaf(q[i], __bfloat162float(k[i]), d);
-    }
-    return d;
 }
 
 template <typename T>
@@ -238,65 +208,6 @@ GB_EXPORT int gb_sigmoid_attention_rows(const void* q, void* out, int dtype, con
 // depends on its position and the window alone. A value row must be 64, 128, 256 or 512 bytes.
 // ----------------------------------------------------------------------------------------------
 constexpr int SAD_WARPS = 8;
-
-template <typename T> struct SadPiece;                 // 16 bytes of a value row as floats
-template <> struct SadPiece<float> {
-    static constexpr int N = 4;
-    static __device__ __forceinline__ void unpack(const uint4& raw, float (&f)[4]) {
-        f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
-    }
-};
-template <> struct SadPiece<__nv_bfloat16> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void unpack(const uint4& raw, float (&f)[8]) {
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const float2 v = __bfloat1622float2(p[t]);
-            f[2 * t] = v.x;
-            f[2 * t + 1] = v.y;
-        }
-    }
-};
-
-// NP 16-byte pieces of a key row against the same channels of R queries (q rows D apart): all loads first, then the sums
-template <typename T, int R, int NP>
-__device__ __forceinline__ void sad_dot_pieces(const float* __restrict__ q, int D, const T* __restrict__ k, float (&out)[R]) {
-    constexpr int PN = SadPiece<T>::N;
-    uint4 raw[NP];
-#pragma unroll
-    for (int c = 0; c < NP; ++c) raw[c] = *reinterpret_cast<const uint4*>(k + c * PN);
-#pragma unroll
-    for (int c = 0; c < NP; ++c) {
-        float f[PN];
-        SadPiece<T>::unpack(raw[c], f);
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int e = 0; e < PN; ++e) out[r] = fmaf(q[r * D + c * PN + e], f[e], out[r]);
-    }
-}
-
-// q . k for R query heads at once (q: R rows of D floats in shared memory), the key row read once
-template <typename T, int R>
-__device__ __forceinline__ void sad_dots(const float* __restrict__ q, const T* __restrict__ k, int D, float (&out)[R]) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) out[r] = 0.f;
-    constexpr int PN = SadPiece<T>::N;
-    if (D % PN == 0 && ((uintptr_t)k & 15) == 0) {
-        // a key row's loads are the critical path of a chunk: eight 16-byte pieces in flight together, then four, then single
-        int i = 0;
-        for (; i + 8 * PN <= D; i += 8 * PN) sad_dot_pieces<T, R, 8>(q + i, D, k + i, out);
-        for (; i + 4 * PN <= D; i += 4 * PN) sad_dot_pieces<T, R, 4>(q + i, D, k + i, out);
-        for (; i < D; i += PN) sad_dot_pieces<T, R, 1>(q + i, D, k + i, out);
-    } else {
-        for (int i = 0; i < D; ++i) {
-            const float kv = gb_to_float(k[i]);
-#pragma unroll
-            for (int r = 0; r < R; ++r) out[r] = fmaf(q[r * D + i], kv, out[r]);
-        }
-    }
-}
 
 template <typename T, int LPK, int R>
 __global__ void __launch_bounds__(SAD_WARPS * 32) sigmoid_attention_decode_kernel(
@@ -443,12 +354,6 @@ GB_EXPORT int gb_sigmoid_attention_decode(const void* q, void* out, int dtype, c
 // on the other keys. Head sizes 32, 64 or 128 for keys and for values, in any combination.
 // ----------------------------------------------------------------------------------------------
 constexpr int SAT_BM = 64, SAT_BN = 64;
-
-__device__ __forceinline__ void sat_cp16(void* smem, const void* gmem, bool valid) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
-}
 
 template <int D, int V>
 __global__ void __launch_bounds__(128) sigmoid_attention_tiles_kernel(

@@ -127,6 +127,12 @@ class StepContext:
         self.prepared_norm = None         # parts.base.PreparedNorm: what the last such product left for that norm
         # A wiring that norms a branch before it joins the residual hands the part a blank buffer instead of the residual:
         self.overwrite_output = False     # True: the part's last product stores into the tensor it was given, not adds
+        # ... and may take over a bias that the part's last product would add to every row (the down projection's):
+        self.accepts_output_bias = False
+        self.output_bias = None
+        # A wiring whose branches read the residual as it is keeps the rows in the activation dtype that the kernel which
+        # completed them wrote beside them: (address of the residual, rows, the copy), see parts/block.py
+        self.residual_copy = None
         # A wiring over several residual streams leaves the fold of a branch's output into the streams to the kernel
         # that reads the streams next: (y, mix, write), see parts/block.py
         self.pending_fold = None

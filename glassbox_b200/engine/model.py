@@ -117,7 +117,7 @@ class DecoderModel:
 
     def _forward(self, ctx, x, in_program: bool) -> torch.Tensor:
         n, d = ctx.n, self.config.hidden_size
-        ctx.next_norm = ctx.norm_after_layer = ctx.prepared_norm = ctx.pending_fold = None
+        ctx.next_norm = ctx.norm_after_layer = ctx.prepared_norm = ctx.pending_fold = ctx.residual_copy = None
         self.embed.forward(ctx, ctx.tokens, x)
         streams = self.config.residual_streams
         if streams:

@@ -75,7 +75,10 @@ _SIGNATURES = {
     "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
     "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "gb_step_io": [_P, _P, _LL, _P, _P, _P, _LL, _P],
-    "gb_rmsnorm_add": [_P, _LL, _P, _P, _LL, _I, _I, _F, _P],
+    "gb_rmsnorm_add": [_P, _LL, _P, _P, _LL, _I, _I, _F, _P, _P, _I, _P],
+    "gb_cast_rows": [_P, _LL, _P, _P, _I, _I, _I, _P],
+    "gb_add_bias": [_P, _LL, _P, _I, _I, _P],
+    "gb_clamped_glu": [_P, _I, _LL, _P, _F, _F, _P, _I, _I, _I, _P],
     "gb_relu2": [_P, _P, _I, _LL, _P],
     "gb_scale": [_P, _LL, _F, _P],
     "gb_gated_head_norm": [_P, _P, _LL, _P, _P, _I, _I, _I, _I, _F, _P],
@@ -94,19 +97,25 @@ _SIGNATURES = {
     "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "gb_streams_broadcast": [_P, _P, _I, _I, _I, _P],
     "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _I, _P, _LL, _P, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
-    "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P],
+    "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P, _P, _LL,
+                              _P, _P],
+    "gb_sink_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_sink_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_sink_attention_decode_supported": [_I],
+    "gb_sink_attention_tiles_supported": [_I, _I],
+    "gb_sink_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sigmoid_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sigmoid_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sigmoid_attention_decode_supported": [_I],
     "gb_sigmoid_attention_tiles_supported": [_I, _I],
     "gb_sigmoid_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_mingru_scan": [_P, _LL, _P, _P, _P, _LL, _LL, _P, _LL, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    "gb_moe_route": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P],
+    "gb_moe_route": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P, _I, _P],
     "gb_moe_expert_rows": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P],
-    "gb_moe_expert_halves": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P],
+    "gb_moe_expert_halves": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _F, _P],
     "gb_moe_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P],
     "gb_moe_grouped_supported": [_I, _I],
-    "gb_moe_grouped_gemm": [_P, _LL, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _P],
+    "gb_moe_grouped_gemm": [_P, _LL, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _I, _F, _F, _P],
     "gb_moe_combine": [_P, _P, _I, _P, _LL, _P, _P, _P, _LL, _I, _I, _I, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
@@ -849,13 +858,46 @@ def resolve_tokens(tokens: torch.Tensor, token_slots: torch.Tensor, last_token: 
 
 
 # ------------------------------------------------------------------ branches that are normed before they join the residual
-def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, x: torch.Tensor, eps: float) -> None:
-    """x[r, :] += gain * y[r, :] / sqrt(mean(y[r, :]^2) + eps); everything float32."""
-    _cuda(y, gain, x)
+def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, x: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None,
+                copy: Optional[torch.Tensor] = None) -> None:
+    """x[r, :] += gain * y[r, :] / sqrt(mean(y[r, :]^2) + eps); everything float32. ``bias`` (float32 [d]) is added to
+    y first (y itself is left as it is); ``copy`` ([n, d], float32 or bfloat16, contiguous) receives the new x."""
+    _cuda(y, gain, x, bias, copy)
     n, d = x.shape
     assert y.shape == (n, d) and y.dtype == x.dtype == gain.dtype == torch.float32 and gain.numel() == d
     assert y.stride(1) == 1 and x.stride(1) == 1
-    _call("gb_rmsnorm_add", _ptr(y), y.stride(0), _ptr(gain), _ptr(x), x.stride(0), n, d, float(eps), _stream())
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == d)
+    assert copy is None or (copy.shape == (n, d) and copy.is_contiguous())
+    _call("gb_rmsnorm_add", _ptr(y), y.stride(0), _ptr(gain), _ptr(x), x.stride(0), n, d, float(eps), _ptr(bias), _ptr(copy),
+          _dt(copy) if copy is not None else 0, _stream())
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = x[rows[r], :] (all rows in order, if ``rows`` is None): float32 rows in ``out``'s dtype, rounded once."""
+    _cuda(x, out, rows)
+    n, d = out.shape
+    assert x.dtype == torch.float32 and x.shape[1] == d and x.stride(1) == 1 and out.is_contiguous()
+    assert (rows is None and x.shape[0] >= n) or (rows is not None and rows.dtype == torch.int32 and rows.numel() >= n)
+    _call("gb_cast_rows", _ptr(x), x.stride(0), _ptr(rows), _ptr(out), _dt(out), n, d, _stream())
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[r, :] += bias; float32."""
+    _cuda(y, bias)
+    n, d = y.shape
+    assert y.dtype == bias.dtype == torch.float32 and bias.numel() == d and y.stride(1) == 1
+    _call("gb_add_bias", _ptr(y), y.stride(0), _ptr(bias), n, d, _stream())
+
+
+def clamped_glu(gate_up: torch.Tensor, bias: Optional[torch.Tensor], limit: float, slope: float, act: torch.Tensor) -> None:
+    """act[r, f] = g * sigmoid(slope * g) * (u + 1) with g = min(gate_up[r, f] + bias[f], limit) and u = clamp(gate_up[r, ff + f]
+    + bias[ff + f], -limit, limit), formed in float32; ``gate_up`` [n, 2 ff] float32 or bfloat16, ``bias`` float32 [2 ff] or None."""
+    _cuda(gate_up, bias, act)
+    n, ff = act.shape
+    assert gate_up.shape == (n, 2 * ff) and gate_up.stride(1) == 1 and act.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * ff)
+    _call("gb_clamped_glu", _ptr(gate_up), _dt(gate_up), gate_up.stride(0), _ptr(bias), float(limit), float(slope), _ptr(act), _dt(act),
+          n, ff, _stream())
 
 
 def relu2(h: torch.Tensor, out: torch.Tensor) -> None:
@@ -1159,11 +1201,19 @@ def streams_step(xs: torch.Tensor, streams: int, *, fold=None, read: Optional[to
 def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                        positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                        heads: int, kv_heads: int, dim: int, vdim: int, rot: int, eps: float, page_size: int, write_kv: bool,
-                       status: torch.Tensor) -> None:
+                       status: torch.Tensor, values_out: Optional[torch.Tensor] = None, values_in: Optional[torch.Tensor] = None,
+                       value_mix: Optional[torch.Tensor] = None) -> None:
     """From the float32 sums of the stacked projection q | k | v: RMS norm of every query and key head over ``dim`` (one
     gain for the query heads, one for the key heads; None: no norm), rotation of the first ``rot`` channels in neighbouring pairs by
-    float32(position) * inv_freq[i], q into ``q_out`` [n, heads * dim], k and v into the paged cache at each row's slot."""
-    _cuda(qkv, q_gain, k_gain, inv_freq, positions, slots, q_out, kcache, vcache, status)
+    float32(position) * inv_freq[i], q into ``q_out`` [n, heads * dim], k and v into the paged cache at each row's slot.
+    With ``values_in`` (float32 [n, kv_heads * vdim]) a row's v becomes (1 - value_mix) v + value_mix values_in[row] first
+    (``value_mix`` one float32 number on the device); ``values_out`` (same shape) receives the row's v as it is stored."""
+    _cuda(qkv, q_gain, k_gain, inv_freq, positions, slots, q_out, kcache, vcache, status, values_out, values_in, value_mix)
+    for t in (values_out, values_in):
+        assert t is None or (t.dtype == torch.float32 and t.shape == (qkv.shape[0], kv_heads * vdim) and t.stride(1) == 1)
+    assert values_out is None or values_in is None or values_out.stride(0) == values_in.stride(0)
+    assert values_in is None or (value_mix is not None and value_mix.dtype == torch.float32 and value_mix.numel() == 1)
+    ld_values = (values_out if values_out is not None else values_in).stride(0) if (values_out is not None or values_in is not None) else 0
     n = qkv.shape[0]
     assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == (heads + kv_heads) * dim + kv_heads * vdim
     for gain in (q_gain, k_gain):
@@ -1173,7 +1223,8 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
     assert rot == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot // 2)
     _call("gb_qk_norm_rope_write", _ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _ptr(positions), _ptr(slots),
           _ptr(q_out), _ptr(kcache), _ptr(vcache), _dt(q_out), n, heads, kv_heads, dim, vdim, rot, float(eps), page_size,
-          kcache.shape[0] * page_size, 1 if write_kv else 0, _ptr(status), _stream())
+          kcache.shape[0] * page_size, 1 if write_kv else 0, _ptr(status), _ptr(values_out), _ptr(values_in), ld_values,
+          _ptr(value_mix) if values_in is not None else 0, _stream())
 
 
 def sigmoid_attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
@@ -1232,6 +1283,74 @@ def sigmoid_attention_tiles(q: torch.Tensor, out: torch.Tensor, kcache: torch.Te
           kv_heads, dim, vdim, page_size, kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
 
 
+# ------------------------------------------------------- softmax attention with a distance bias, a sink and an output gate
+def _sink_args(r1, r2, sink, gate, heads):
+    assert (r1 is None) == (r2 is None)
+    for t in (r1, r2, sink):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == heads)
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[1] == heads and gate.stride(1) == 1)
+    return _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0
+
+
+def sink_attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                        row_seq: torch.Tensor, positions: torch.Tensor, *, r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
+                        sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int,
+                        page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """out[row, head, :] = sigmoid(gate[row, head]) * sum over the row's visible keys j of w_j v_j, the weights a softmax of
+    s_j = q . k_j * scale - r1[head] * ln(1 + r2[head] * distance) whose denominator also holds exp(sink[head]). ``r1``/``r2``,
+    ``sink`` (float32 [heads]) and ``gate`` (float32 logits [n, heads], rows may be strided) are each optional. One warp per
+    (row, head); any row, both dtypes."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, r1, r2, sink, gate, status)
+    n = q.shape[0]
+    assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and block_tables.is_contiguous()
+    _call("gb_sink_attention_rows", _ptr(q), _ptr(out), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(row_seq), _ptr(positions), *_sink_args(r1, r2, sink, gate, heads), n, heads, kv_heads, dim, vdim, page_size,
+          kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
+
+
+def sink_attention_decode_supported(dtype: torch.dtype, vdim: int) -> bool:
+    return dtype in _DT and bool(lib().gb_sink_attention_decode_supported(vdim * (4 if dtype == torch.float32 else 2)))
+
+
+def sink_attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                          row_seq: torch.Tensor, positions: torch.Tensor, *, r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
+                          sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int,
+                          page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """``sink_attention_rows`` for single decoded tokens: a block of eight warps per (row, head) that share the row's keys,
+    each with a running maximum of its own, and meet in a fixed order; a value row must be 64, 128, 256 or 512 bytes
+    (``sink_attention_decode_supported``)."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, r1, r2, sink, gate, status)
+    n = q.shape[0]
+    assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and block_tables.is_contiguous()
+    _call("gb_sink_attention_decode", _ptr(q), _ptr(out), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+          block_tables.shape[1], _ptr(row_seq), _ptr(positions), *_sink_args(r1, r2, sink, gate, heads), n, heads, kv_heads, dim, vdim,
+          page_size, kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
+
+
+def sink_attention_tiles_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().gb_sink_attention_tiles_supported(dim, vdim))
+
+
+def sink_attention_tiles(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                         seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, max_rows_per_seq: int, *,
+                         r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                         gate: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int, page_size: int, scale: float,
+                         window: Optional[int], status: torch.Tensor) -> None:
+    """``sink_attention_rows`` for runs of consecutive rows (prompt portions) in bfloat16 on the tensor cores: a block
+    takes 64 rows of one request and one head; ``max_rows_per_seq`` bounds the rows a request brings (it sizes the grid)."""
+    _cuda(q, out, kcache, vcache, block_tables, seq_first_row, seq_start_pos, r1, r2, sink, gate, status)
+    n = q.shape[0]
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype == torch.bfloat16
+    assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
+    assert block_tables.is_contiguous() and seq_first_row.shape[0] == seq_start_pos.shape[0] + 1
+    _call("gb_sink_attention_tiles", _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(seq_first_row), _ptr(seq_start_pos), *_sink_args(r1, r2, sink, gate, heads), seq_start_pos.shape[0],
+          max(int(max_rows_per_seq), 1), heads, kv_heads, dim, vdim, page_size, kcache.shape[0], float(scale),
+          int(window) if window else 0, _ptr(status), _stream())
+
+
 # ------------------------------------------------------------------------------------------------ minGRU
 def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, state_off: int, out: torch.Tensor,
                 seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, width: int, write_state: bool,
@@ -1253,10 +1372,14 @@ def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, 
 # ------------------------------------------------------------------------------------------- routed experts
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_gate: Optional[torch.Tensor],
               positions: torch.Tensor, top: int, groups: int, keep: int, route_scale: float, choice: torch.Tensor,
-              weight: torch.Tensor, gate: Optional[torch.Tensor]) -> None:
+              weight: torch.Tensor, gate: Optional[torch.Tensor], router_bias: Optional[torch.Tensor] = None,
+              softmax_chosen: bool = False) -> None:
     """Per row: float32 router logits, sigmoid scores, the ``top`` experts by score + correction among the ``keep`` best of
-    ``groups`` runs of neighbouring experts, weights score * route_scale; ``gate`` = sigmoid(w_gate . h) per row."""
-    _cuda(h, w_router, correction, w_gate, positions, choice, weight, gate)
+    ``groups`` runs of neighbouring experts, weights score * route_scale; ``gate`` = sigmoid(w_gate . h) per row. With
+    ``softmax_chosen`` the ``top`` largest logits (plus ``router_bias``, float32 [experts]) win and the weights are the
+    softmax over the chosen logits alone."""
+    _cuda(h, w_router, correction, w_gate, positions, choice, weight, gate, router_bias)
+    assert router_bias is None or (softmax_chosen and router_bias.dtype == torch.float32 and router_bias.numel() == w_router.shape[0])
     n, d = h.shape
     E = w_router.shape[0]
     assert h.is_contiguous() and w_router.dtype == torch.float32 and w_router.shape == (E, d) and w_router.is_contiguous()
@@ -1266,7 +1389,7 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     assert weight.dtype == torch.float32 and weight.shape == (n, top) and weight.is_contiguous()
     assert gate is None or (gate.dtype == torch.float32 and gate.numel() >= n)
     _call("gb_moe_route", _ptr(h), _dt(h), d, _ptr(w_router), _ptr(correction), _ptr(w_gate), _ptr(positions), n, E, top, groups, keep,
-          float(route_scale), _ptr(choice), _ptr(weight), _ptr(gate), _stream())
+          float(route_scale), _ptr(choice), _ptr(weight), _ptr(gate), _ptr(router_bias), 1 if softmax_chosen else 0, _stream())
 
 
 def moe_expert_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
@@ -1285,19 +1408,21 @@ def moe_expert_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, e
 
 
 def moe_expert_halves(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
-                       positions: torch.Tensor, act: torch.Tensor, pair: torch.Tensor) -> None:
+                       positions: torch.Tensor, act: torch.Tensor, pair: torch.Tensor, unit=None) -> None:
     """``moe_expert_rows`` as two launches of many blocks per (row, choice), for a handful of rows: act float32 [n, top * ff]
-    receives relu(W_up[e] h)^2, pair float32 [n, top * d] the experts' outputs."""
+    receives relu(W_up[e] h)^2, pair float32 [n, top * d] the experts' outputs. ``unit`` = (limit, slope): the experts are
+    clamped gated units, ``w_up`` [experts * 2 ff, d] holds gate row f and up row f of an expert as its rows 2f and 2f + 1,
+    and act receives g * sigmoid(slope g) * (u + 1)."""
     _cuda(h, w_up, w_down, choice, positions, act, pair)
     n, d = h.shape
     top = choice.shape[1]
-    ff = w_up.shape[0] // experts
+    ff = w_up.shape[0] // experts // (2 if unit else 1)
     assert h.dtype == w_up.dtype == w_down.dtype and h.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
-    assert w_up.shape == (experts * ff, d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
+    assert w_up.shape == (experts * ff * (2 if unit else 1), d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
     assert act.dtype == pair.dtype == torch.float32 and act.shape == (n, top * ff) and pair.shape == (n, top * d)
     assert act.is_contiguous() and pair.is_contiguous()
     _call("gb_moe_expert_halves", _ptr(h), _dt(h), d, _ptr(w_up), _ptr(w_down), ff, _ptr(choice), _ptr(positions), n, experts, top,
-          _ptr(act), _ptr(pair), _stream())
+          _ptr(act), _ptr(pair), 1 if unit else 0, float(unit[0]) if unit else 0.0, float(unit[1]) if unit else 0.0, _stream())
     global launch_count
     launch_count += 1
 
@@ -1307,27 +1432,29 @@ def moe_grouped_supported(dtype: torch.dtype, d: int, ff: int) -> bool:
 
 
 def moe_experts_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
-                        positions: torch.Tensor, tables: torch.Tensor, act: torch.Tensor, pair: torch.Tensor) -> None:
+                        positions: torch.Tensor, tables: torch.Tensor, act: torch.Tensor, pair: torch.Tensor, unit=None) -> None:
     """The chosen experts of many rows as grouped products on the tensor cores (bfloat16): the (row, choice) pairs are
     sorted by expert (``tables`` int32 [2 * (experts + 1) + n * top] is the sort's scratch), then one launch computes
     act = relu(W_up[e] h)^2 for all pairs (bfloat16 [n, top * ff], in sorted order) and one pair = W_down[e] act
-    (float32 [n, top * d], in pair order)."""
+    (float32 [n, top * d], in pair order). ``unit`` as in ``moe_expert_halves``: the up product then has 2 ff outputs per
+    expert, and its epilogue forms one unit from every two neighbours."""
     _cuda(h, w_up, w_down, choice, positions, tables, act, pair)
     n, d = h.shape
     top = choice.shape[1]
-    ff = w_up.shape[0] // experts
+    up_rows = w_up.shape[0] // experts
+    ff = up_rows // (2 if unit else 1)
     P = n * top
     assert h.dtype == w_up.dtype == w_down.dtype == act.dtype == torch.bfloat16 and pair.dtype == torch.float32
     assert h.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and act.is_contiguous() and pair.is_contiguous()
-    assert w_up.shape == (experts * ff, d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
+    assert w_up.shape == (experts * up_rows, d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
     assert act.shape == (n, top * ff) and pair.shape == (n, top * d)
     assert tables.dtype == torch.int32 and tables.is_contiguous() and tables.numel() >= 2 * (experts + 1) + P
     offsets, tile_start, order = tables[:experts + 1], tables[experts + 1:2 * (experts + 1)], tables[2 * (experts + 1):]
     _call("gb_moe_sort", _ptr(choice), _ptr(positions), n, experts, top, _ptr(offsets), _ptr(tile_start), _ptr(order), _stream())
-    _call("gb_moe_grouped_gemm", _ptr(h), d, _ptr(w_up), ff, d, _ptr(order), _ptr(offsets), _ptr(tile_start), experts, top, P,
-          _ptr(act), ff, 1, _stream())
+    _call("gb_moe_grouped_gemm", _ptr(h), d, _ptr(w_up), up_rows, d, _ptr(order), _ptr(offsets), _ptr(tile_start), experts, top, P,
+          _ptr(act), ff, 1, 1 if unit else 0, float(unit[0]) if unit else 0.0, float(unit[1]) if unit else 0.0, _stream())
     _call("gb_moe_grouped_gemm", _ptr(act), ff, _ptr(w_down), d, ff, _ptr(order), _ptr(offsets), _ptr(tile_start), experts, top, P,
-          _ptr(pair), d, 0, _stream())
+          _ptr(pair), d, 0, 0, 0.0, 0.0, _stream())
 
 
 def moe_combine(pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],

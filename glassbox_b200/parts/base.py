@@ -96,12 +96,17 @@ class Norm(Part):
         None (the norm then always runs as its own kernel)."""
         return None
 
-    def add_normed(self, ctx, y, x) -> None:
+    def add_normed(self, ctx, y, x, bias=None, copy=None) -> None:
         """x += norm(y), both float32 [n, d]: a branch whose output is normed before it joins the residual stream.
-        The default goes through ``forward``; norms with a kernel for it override this."""
+        ``bias`` (float32 [d], optional) is added to y first; ``copy`` (activation dtype [n, d], optional) receives the new
+        x. The default goes through ``forward``; norms with a kernel for it override this."""
+        if bias is not None:
+            y += bias
         tmp = ctx.scratch("normed_branch", tuple(y.shape), torch.float32)
         self.forward(ctx, y, tmp)
         x += tmp
+        if copy is not None:
+            copy.copy_(x)
 
 
 class PreparedNorm:

@@ -2,7 +2,8 @@
 
 "pre_norm" is x += mixer(norm(x)); x += ffn(norm(x)), with no norms after the parts
 (crates/glassbox-core/src/model.rs:251-348; a layer may lack the feed-forward). "sandwich_norm" norms each branch on the
-way out as well: x += post(mixer(norm(x))); x += post(ffn(norm(x))). "hyper_connections" keeps the residual as several
+way out as well: x += post(mixer(norm(x))); x += post(ffn(norm(x))). "branch_norm" norms them on the way out only: the
+branches read the residual itself, x += post(mixer(x)); x += post(ffn(x)). "hyper_connections" keeps the residual as several
 streams x_1 .. x_S per token: a branch reads u = sum_s read[s] x_s through its norm, and its output y comes back into all
 streams at once, x_t <- sum_s mix[s, t] x_s + write[t] y. The arrangement is looked up by name, so another
 wiring (post-norm, parallel branches) is another registered class.
@@ -14,6 +15,7 @@ import torch
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import DeferredNorm, Part, build_part, register_part
+from .norm import ResidualItself
 
 
 class PreNormBlock(Part):
@@ -110,6 +112,82 @@ class SandwichNormBlock(Part):
             after_mixer()
         if self.ffn is not None:
             self._branch(ctx, self.ffn, self.ffn_norm, self.ffn_post_norm, x, lambda h, out: self.ffn.forward(ctx, h, out))
+
+
+class BranchNormBlock(Part):
+    """x += post_norm(mixer(x)), then x += post_norm(ffn(x)) (the second half only if the layer has a feed-forward): the
+    branches read the residual itself, in the activation dtype (a float32 engine hands them the residual where it lies),
+    and only their outputs are normed. A branch gets a float32 buffer for its output, as in the sandwich wiring, and may
+    leave a bias of its last product to the post norm (``ctx.accepts_output_bias`` / ``ctx.output_bias``). The kernel that
+    norms a branch into the residual also writes the new residual rows in the activation dtype when the next reader wants
+    them as they are (the feed-forward of this layer; the mixer of the next, if that layer is wired like this one: the
+    model says so through ``ctx.norm_after_layer``), so that a branch costs one launch beside its own."""
+    launches_through_kernels_only = False      # (clearing the buffer for a part that adds is a torch operation)
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        if spec.mixer_post_norm is None or (spec.ffn is not None and spec.ffn_post_norm is None):
+            raise ValueError("a branch_norm layer needs a norm behind its mixer and behind its feed-forward")
+        if spec.mixer_norm is not None or spec.ffn_norm is not None:
+            raise ValueError("a branch_norm layer has no norm in front of its branches")
+        self.hidden_size = hidden_size
+        self.entry = ResidualItself(hidden_size=hidden_size)
+        self.mixer = build_part("mixer", spec.mixer, hidden_size=hidden_size)
+        self.mixer_post_norm = build_part("norm", spec.mixer_post_norm, hidden_size=hidden_size)
+        self.ffn = self.ffn_post_norm = None
+        if spec.ffn is not None:
+            self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
+            self.ffn_post_norm = build_part("norm", spec.ffn_post_norm, hidden_size=hidden_size)
+
+    def sub_parts(self):
+        parts = {"mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.ffn is not None:
+            parts.update({"ffn": self.ffn, "ffn_post_norm": self.ffn_post_norm})
+        return parts
+
+    def entry_norm(self):
+        return self.entry
+
+    def _input(self, ctx, x):
+        """The residual rows as a branch reads them."""
+        ready, ctx.residual_copy = getattr(ctx, "residual_copy", None), None
+        if x.dtype == ctx.dtype:
+            return x
+        if ready is not None and ready[0] == x.data_ptr() and ready[1] == x.shape[0]:
+            return ready[2]
+        h = ctx.scratch("h", tuple(x.shape))
+        self.entry.forward(ctx, x, h)
+        return h
+
+    def _branch(self, ctx, part, post, x, run, copy_after: bool) -> None:
+        h = self._input(ctx, x)
+        branch = ctx.scratch("branch", tuple(x.shape), torch.float32)
+        ctx.overwrite_output = bool(part.can_overwrite_output)
+        if not ctx.overwrite_output:
+            branch.zero_()
+        ctx.accepts_output_bias, ctx.output_bias = True, None
+        try:
+            run(h, branch)
+        finally:
+            ctx.overwrite_output = ctx.accepts_output_bias = False
+        bias, ctx.output_bias = ctx.output_bias, None
+        copy = ctx.scratch("h", tuple(x.shape)) if copy_after and x.dtype != ctx.dtype else None
+        post.add_normed(ctx, branch, x, bias=bias, copy=copy)
+        ctx.prepared_norm = None         # x has changed behind the back of whatever was prepared from it
+        if copy is not None:
+            ctx.residual_copy = (x.data_ptr(), x.shape[0], copy)
+
+    def forward(self, ctx, x, cache, writes_cache: bool, after_mixer=None) -> None:
+        ctx.next_norm = None             # no product of this layer completes residual rows: nothing to prepare
+        next_reads_as_is = isinstance(getattr(ctx, "norm_after_layer", None), ResidualItself)
+        self._branch(ctx, self.mixer, self.mixer_post_norm, x,
+                     lambda h, out: self.mixer.forward(ctx, h, out, cache, writes_cache),
+                     copy_after=self.ffn is not None or next_reads_as_is)
+        if after_mixer is not None:
+            after_mixer()
+        if self.ffn is not None:
+            self._branch(ctx, self.ffn, self.ffn_post_norm, x, lambda h, out: self.ffn.forward(ctx, h, out),
+                         copy_after=next_reads_as_is)
 
 
 class StreamMixing(Part):
@@ -209,6 +287,8 @@ def collapse_streams(ctx, xs, streams: int, norm, out, rows=None, total=None) ->
 
 register_part("arrangement", "hyper_connections",
               lambda kind, *, layer_spec, hidden_size: HyperConnectionBlock(layer_spec, hidden_size=hidden_size), replace=True)
+register_part("arrangement", "branch_norm",
+              lambda kind, *, layer_spec, hidden_size: BranchNormBlock(layer_spec, hidden_size=hidden_size), replace=True)
 register_part("arrangement", "sandwich_norm",
               lambda kind, *, layer_spec, hidden_size: SandwichNormBlock(layer_spec, hidden_size=hidden_size), replace=True)
 register_part("arrangement", "pre_norm", lambda kind, *, layer_spec, hidden_size: PreNormBlock(layer_spec, hidden_size=hidden_size),

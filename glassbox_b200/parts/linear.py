@@ -135,3 +135,10 @@ def relu2_linear(ctx, a, w: torch.Tensor, act: torch.Tensor) -> bool:
         kernels.gemm_tc(x, w, act, False, ctx.status, relu2=True)
         return True
     return False
+
+
+def clamped_glu_linear(ctx, a, w_gate_up: torch.Tensor, bias, limit: float, slope: float, act: torch.Tensor) -> bool:
+    """act = g * sigmoid(slope * g) * (u + 1) with g = min(a Wgate^T + b_gate, limit), u = clamp(a Wup^T + b_up, -limit,
+    limit) in one kernel (the unit in the product's epilogue, from the float32 sums) when a kernel with that epilogue takes
+    the operands; returns False (and does nothing) otherwise, and the caller runs the product and the unit separately."""
+    return False

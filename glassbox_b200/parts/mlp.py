@@ -3,10 +3,12 @@ then up rows stacked in one matrix, SiLU as g / (1 + exp(-g)), no bias
 (crates/glassbox-core/src/model.rs:327-344; stacking crates/glassbox-core/src/load.rs:62-65)."""
 from __future__ import annotations
 
+import torch
+
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import FeedForward, register_part
-from .linear import gated_linear, linear, relu2_linear
+from .linear import clamped_glu_linear, gated_linear, linear, relu2_linear
 
 
 class SwiGlu(FeedForward):
@@ -57,5 +59,46 @@ class SquaredRelu(FeedForward):
         linear(ctx, act, self.params["w_down"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
 
+class ClampedGlu(FeedForward):
+    """Dense gated feed-forward with clamped branches: g = min(x Wgate^T + b_gate, limit), u = clamp(x Wup^T + b_up, -limit,
+    limit), residual += (g * sigmoid(slope * g) * (u + 1)) Wdown^T + b_down. Gate rows then up rows stacked in one matrix
+    (and one bias vector). The clamps, the sigmoid and the product are formed in float32 from the float32 sums of the first
+    product. A wiring that norms the branch takes the down projection's bias over (``ctx.accepts_output_bias``) and adds
+    it on its way over the rows; otherwise a small kernel adds it."""
+    launches_through_kernels_only = True
+    can_overwrite_output = True
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        if not spec.limit > 0:
+            raise ValueError(f"limit {spec.limit} must be positive")
+        self.hidden_size = hidden_size
+        self.inter = spec.intermediate_size
+
+    def param_specs(self):
+        d, i = self.hidden_size, self.inter
+        specs = {"w_gate_up": ParamSpec((2 * i, d), pieces=(i, i)), "w_down": ParamSpec((d, i))}
+        if self.spec.bias:
+            specs["b_gate_up"] = ParamSpec((2 * i,), role="gain", pieces=(i, i), init=(0.0, 0.5))
+            specs["b_down"] = ParamSpec((d,), role="gain", init=(0.0, 0.5))
+        return specs
+
+    def forward(self, ctx, h, residual) -> None:
+        n, s, p = h.shape[0], self.spec, self.params
+        act = ctx.scratch("act", (n, self.inter))
+        if not clamped_glu_linear(ctx, h, p["w_gate_up"], p.get("b_gate_up"), s.limit, s.slope, act):
+            gate_up = ctx.scratch("gate_up32", (n, 2 * self.inter), torch.float32)
+            linear(ctx, h, p["w_gate_up"], gate_up)
+            kernels.clamped_glu(gate_up, p.get("b_gate_up"), s.limit, s.slope, act)
+        overwrite = getattr(ctx, "overwrite_output", False)
+        linear(ctx, act, p["w_down"], residual, accumulate=not overwrite)
+        if "b_down" in p:
+            if overwrite and getattr(ctx, "accepts_output_bias", False):
+                ctx.output_bias = p["b_down"]
+            else:
+                kernels.add_bias(residual, p["b_down"])
+
+
+register_part("ffn", "clamped_glu", ClampedGlu, replace=True)
 register_part("ffn", "swiglu", SwiGlu, replace=True)
 register_part("ffn", "relu2", SquaredRelu, replace=True)

@@ -24,8 +24,8 @@ class RmsNorm(Norm):
     def as_rms(self):
         return self.params["weight"], self.eps
 
-    def add_normed(self, ctx, y, x) -> None:
-        kernels.rmsnorm_add(y, self.params["weight"], x, self.eps)
+    def add_normed(self, ctx, y, x, bias=None, copy=None) -> None:
+        kernels.rmsnorm_add(y, self.params["weight"], x, self.eps, bias=bias, copy=copy)
 
 
 class UnitOffsetRmsNorm(RmsNorm):
@@ -36,6 +36,20 @@ class UnitOffsetRmsNorm(RmsNorm):
     def bind(self, params) -> None:
         super().bind(params)
         self.params["weight"] = (self.params["weight"].float() + 1.0).contiguous()
+
+
+class ResidualItself(Norm):
+    """No norm at all: a branch that reads the residual as it is gets its rows in the activation dtype (rounded once). It
+    stands where a wiring names "the norm that reads the residual next", so that whoever completes the residual rows can
+    tell that the next reader wants them as they are."""
+    launches_through_kernels_only = True
+
+    def __init__(self, spec=None, *, hidden_size: int = 0):
+        super().__init__(spec)
+        self.hidden_size = hidden_size
+
+    def forward(self, ctx, x, out, rows=None) -> None:
+        kernels.cast_rows(x, out, rows)
 
 
 class LayerNorm(Norm):
@@ -62,6 +76,7 @@ class LayerNorm(Norm):
         kernels.streams_step(x, 1, norm=self.as_layernorm(), h=out, rows=rows)
 
 
+register_part("norm", "none", ResidualItself, replace=True)
 register_part("norm", "layernorm", LayerNorm, replace=True)
 register_part("norm", "rmsnorm", RmsNorm, replace=True)
 register_part("norm", "rmsnorm_unit_offset", UnitOffsetRmsNorm, replace=True)

@@ -34,6 +34,14 @@ class Stacked:
 
 
 @dataclass(frozen=True)
+class Ignorable:
+    """File tensors that may be present and are then not read: an architecture that stores a tensor for every layer but
+    uses it only in some names the others here, under the key ``Ignorable.KEY`` of its binding."""
+    names: Tuple[str, ...]
+    KEY = "(ignorable)"
+
+
+@dataclass(frozen=True)
 class Tied:
     """The parameter is the same storage as another parameter (e.g. head = embedding).
     ``ignorable`` names file tensors that may be present and are then not read."""

@@ -15,7 +15,7 @@ from typing import Dict
 
 import torch
 
-from .binding import ParamSpec, Tied
+from .binding import Ignorable, ParamSpec, Tied
 from .safetensors_io import SafetensorsFile, WeightsError
 
 
@@ -45,6 +45,9 @@ def load_parameters(specs: Dict[str, ParamSpec], binding: dict, st: SafetensorsF
     missing, wrong, unbound = [], [], []
     used, ignorable = set(), set()
     plan = {}
+    extra = binding.get(Ignorable.KEY)
+    if isinstance(extra, Ignorable):
+        ignorable.update(extra.names)
     for path, spec in specs.items():
         src = binding.get(path)
         if src is None:
@@ -81,7 +84,7 @@ def load_parameters(specs: Dict[str, ParamSpec], binding: dict, st: SafetensorsF
         if ok:
             plan[path] = (spec, src)
     unexpected = sorted(n for n in st.names() if n not in used and n not in ignorable)
-    extra_bindings = sorted(p for p in binding if p not in specs)
+    extra_bindings = sorted(p for p in binding if p not in specs and p != Ignorable.KEY)
     if missing or wrong or unexpected or unbound or extra_bindings:
         lines = [f"{st.path}: weights do not fit the configuration"]
         if missing:

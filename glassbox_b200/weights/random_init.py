@@ -49,9 +49,9 @@ def random_tensors(raw_config: dict, seed: int, store_dtype: torch.dtype = torch
         if isinstance(src, Tied):
             continue
         assert isinstance(src, Stacked)
-        rows = spec.pieces if len(src.names) > 1 else (spec.shape[0],)
+        rows = spec.pieces if len(src.names) > 1 else (spec.shape[0] if spec.shape else None,)
         for name, r in zip(src.names, rows):
-            shape = (r,) + tuple(spec.shape[1:])
+            shape = (r,) + tuple(spec.shape[1:]) if spec.shape else ()      # (a scalar parameter has no rows)
             g = _generator(seed, name)
             if spec.init is not None and spec.role != "table":
                 t = spec.init[0] + spec.init[1] * torch.randn(shape, generator=g, dtype=torch.float32)
