@@ -479,6 +479,67 @@ def lonorax_workload(args):
     return out
 
 
+# ------------------------------------------------------------------------------------------------ Tagenex beside its neighbours
+#: layer sizes that resemble real models' (random weights): a Tagenex model whose layers are all sliding-window attention
+#: with a sink, a distance bias, value mixing and an output gate, the feed-forwards in turn a dense clamped gated unit of
+#: width ``ff`` and a mixture of 16 such units of width ``ff / 4`` of which four per token (as many multiply-adds per token
+#: as the dense one). Beside it the Llama decoder (the framework's other model of grouped-query softmax attention in every
+#: layer, with a dense gated feed-forward) and Lonorax (its other model of windowed attention and routed experts), both of
+#: the same width, depth and feed-forward width.
+TAGENEX_SIZES = {
+    "w1024": dict(attn=dict(heads=16, kv_heads=4, dim=64, vdim=64), window=1024, moe=dict(experts=16, top=4, ff=1024)),
+    "w2048": dict(attn=dict(heads=32, kv_heads=8, dim=64, vdim=64), window=1024, moe=dict(experts=16, top=4, ff=2048)),
+}
+
+
+def tagenex_raw(size: dict, own: dict) -> dict:
+    from glassbox_b200.models.tagenex import make_tagenex_raw_config
+    layers = []
+    for i in range(size["layers"]):
+        m = dict(own["attn"])
+        m.update(scale=m["dim"] ** -0.5, mask={"size": own["window"]}, v_mix=True)
+        if i % 2:
+            e = own["moe"]
+            mlp = {"kind": "moe", "expert": {"ff": e["ff"], "limit": 7.0}, "router": {"experts": e["experts"], "top": e["top"]}}
+        else:
+            mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return make_tagenex_raw_config(vocab=size["vocab"], width=size["width"], layers=layers)
+
+
+def measure_arm(label: str, args, T: int, ctx: int, K: int, W: int, **kw) -> dict:
+    """Prefill of ``T`` tokens and decode steps at batch 1, 8 and 64 (three timed regions each) of one model."""
+    mb = ModelBench(label, args.dtype, 64, ctx, **kw)
+    try:
+        r = {"weight_mb": round(mb.eng.weight_bytes() / 2 ** 20, 1), "cache_bytes_per_token": mb.eng.cache_bytes_per_token()}
+        m, sd = mean_sd(mb.prefill(T))
+        r["prefill"] = {"ms": round(m, 3), "sd": round(sd, 3), "tokens_per_s": round(T / (m / 1e3))}
+        for b in (1, 8, 64):
+            regions, launches, _ = mb.decode(b, K, W, reps=3)
+            m, sd = mean_sd(regions)
+            r[f"decode_b{b}"] = {"ms_per_step": round(m / K, 4), "sd": round(sd / K, 4), "tokens_per_s": round(b * K / (m / 1e3)),
+                                 "launches_per_step": round(launches / K, 1)}
+        return r
+    finally:
+        mb.close()
+
+
+def tagenex_workload(args):
+    """Prefill and decode throughput of Tagenex models beside the Llama decoder and Lonorax of equal width, depth and
+    feed-forward width; one JSON line. Decode steps end at the context length; three timed regions per point."""
+    T, ctx, K, W = 2048, args.context, min(args.steps, 128), max(args.warmup, 3)
+    out = {"workload": "tagenex", "dtype": args.dtype, "context": ctx, "prefill_tokens": T, "decode_steps": K, "sizes": {}}
+    for name, size in ZURERAX_SIZES.items():
+        llama = dict(num_hidden_layers=size["layers"], hidden_size=size["width"], intermediate_size=size["ff"],
+                     vocab_size=size["vocab"], rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                     max_position_embeddings=8192, **size["llama"])
+        arms = (("tagenex", dict(raw=tagenex_raw(size, TAGENEX_SIZES[name]))), ("llama", dict(shape=llama)),
+                ("lonorax", dict(raw=lonorax_raw(size, LONORAX_SIZES[name]))))
+        out["sizes"][name] = {label: measure_arm(f"{label}-{name}", args, T, ctx, K, W, **kw) for label, kw in arms
+                              if not args.only or label in args.only.split(",")}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -493,13 +554,14 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="only the headline region: no other batches, prefill or e2e")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the other model sizes, the serving workload, the 32-bit path and the CPU baseline")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax", "lonorax"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax", "lonorax", "tagenex"],
                     help="serving: the mixed workload of the 360M configuration (64 requests, prompts 32-2048, outputs "
                          "32-512, prompt portions of 512, a quarter of the requests sharing a 384-token prefix) through "
                          "the scheduler; prints its own JSON line. zurerax: prefill and decode throughput of Zurerax models "
                          "at two widths beside the Llama decoder of equal size; prints its own JSON line. lonorax: the same for "
-                         "Lonorax models beside Zurerax and Llama of equal size")
-    ap.add_argument("--only", default="", help="with --workload lonorax: the arms to run (lonorax,zurerax,llama), with commas")
+                         "Lonorax models beside Zurerax and Llama of equal size; tagenex: the same for Tagenex models beside Llama "
+                         "and Lonorax of equal size")
+    ap.add_argument("--only", default="", help="with --workload lonorax or tagenex: the arms to run (tagenex,lonorax,zurerax,llama), with commas")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -520,6 +582,9 @@ def main():
         return 0
     if args.workload == "lonorax":
         print(json.dumps(lonorax_workload(args)))
+        return 0
+    if args.workload == "tagenex":
+        print(json.dumps(tagenex_workload(args)))
         return 0
     K, W, B, CTX = args.steps, max(args.warmup, 3), args.batch, args.context
     pk = peaks()
