@@ -219,6 +219,26 @@ GB_EXPORT int gb_gemm_stream(const void* x, long long ldx, const float* xres, lo
     return dispatch_stream(a, (N + 15) / 16, mode == WS_GLU_BF16, pdl, stream);
 }
 
+// The gated mode with the clamped unit in the epilogue: W = [gate rows; up rows] (2 N rows), c bfloat16 [M, N] =
+// g * sigmoid(slope * g) * (u + 1) with g = min(x gate^T + bias[:N], limit), u = clamp(x up^T + bias[N:], -limit, limit),
+// formed from the float32 sums. bias (float32 [2 N]) may be nullptr. The other arguments as in gb_gemm_stream.
+GB_EXPORT int gb_gemm_stream_unit(const void* x, long long ldx, const float* xres, long long ldr, const float* gain, float eps,
+                                  const void* w, long long ldw, void* c, long long ldc, int M, int N, int K, const float* bias,
+                                  float limit, float slope, const void* prefetch, long long prefetch_bytes, int pdl,
+                                  cudaStream_t stream) {
+    if (check_common("gb_gemm_stream_unit", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
+    GB_REQUIRE(N % 16 == 0 && limit > 0.f, "gb_gemm_stream_unit: N must be a multiple of 16 and the limit positive");
+    GB_REQUIRE(x != nullptr || gain != nullptr, "gb_gemm_stream_unit: normalising needs a gain");
+    if (M == 0) return 0;
+    StreamArgs a = {};
+    a.X = (const __nv_bfloat16*)x; a.ldx = ldx; a.xres = xres; a.ldr = ldr; a.gain = gain; a.eps = eps;
+    a.W = (const __nv_bfloat16*)w; a.ldw = ldw; a.C = c; a.ldc = ldc; a.mode = WS_UNIT_BF16; a.M = M; a.N = N; a.K = K;
+    a.pair_offset = N;
+    a.unit_bias = bias; a.unit_limit = limit; a.unit_slope = slope;
+    a.prefetch = (const unsigned char*)prefetch; a.prefetch_bytes = prefetch ? prefetch_bytes : 0;
+    return dispatch_stream(a, (N + 15) / 16, true, pdl, stream);
+}
+
 // Stacked QKV projection with rotary encoding and cache write in the epilogue. W = [q rows; k rows; v
 // rows] ((nh + 2 nkv) * hd rows); q_out bfloat16 [M, >= nh*hd] receives the rotated queries; rotated keys
 // and the values go to the cache slot of each row (unless write_kv == 0). hd must be a multiple of 32;

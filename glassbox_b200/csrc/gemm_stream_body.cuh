@@ -10,7 +10,7 @@
 
 namespace cg = cooperative_groups;
 
-enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4, WS_RELU2_BF16 = 5 };
+enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4, WS_RELU2_BF16 = 5, WS_UNIT_BF16 = 6 };
 
 constexpr int WS_PAD = 32;             // padding per activation row: row stride = 16 banks mod 32, so the
                                        // 16-byte operand loads of a quarter-warp never collide
@@ -42,6 +42,10 @@ struct StreamArgs {
     const unsigned char* prefetch;
     long long prefetch_bytes;
     int late_release;         // let the next kernel in the stream go only after this one's own wait (else at its start)
+    // the clamped gated unit (WS_UNIT_BF16): g = min(gate sum + bias[n], limit), u = clamp(up sum + bias[N + n], -limit, limit),
+    // c = bfloat16(g * sigmoid(slope * g) * (u + 1)); unit_bias float32 [2 N] or nullptr
+    const float* unit_bias;
+    float unit_limit, unit_slope;
 };
 
 __device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -454,6 +458,13 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
         } else if (a.mode == WS_GLU_BF16) {
             const float g = v[0] / (1.0f + __expf(-v[0])) * v[1];
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(g);
+        } else if (a.mode == WS_UNIT_BF16) {
+            const float bg = a.unit_bias != nullptr ? __ldg(a.unit_bias + n) : 0.f;
+            const float bu = a.unit_bias != nullptr ? __ldg(a.unit_bias + N + n) : 0.f;
+            const float g = fminf(v[0] + bg, a.unit_limit);
+            const float u = fminf(fmaxf(v[1] + bu, -a.unit_limit), a.unit_limit);
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] =
+                __float2bfloat16_rn(g / (1.0f + __expf(-a.unit_slope * g)) * (u + 1.0f));
         } else if (a.mode == WS_STORE_BF16) {
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(v[0]);
         } else if (a.mode == WS_RELU2_BF16) {       // squared ReLU, from the float32 sum

@@ -57,6 +57,14 @@ struct TcNorm {
     float eps;
 };
 
+// A GATED launch whose unit is the clamped one (limit > 0) instead of silu(gate) * up: with the float32 sums G and U of a
+// gate column and its up column, g = min(G + bias[col], limit), u = clamp(U + bias[gate_rows + col], -limit, limit) and the
+// output is g * sigmoid(slope * g) * (u + 1). bias (float32 [2 * gate_rows]) may be nullptr.
+struct TcUnit {
+    const float* bias;
+    float limit, slope;
+};
+
 constexpr int TC_MAX_STAGES = 8;
 
 struct __align__(8) TcShared {
@@ -93,7 +101,8 @@ template <int BN, bool GATED>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_w, void* __restrict__ C,
                                                            int mode, int M, int N, int K, long long ldc, int gate_rows,
-                                                           int* __restrict__ status, const TcQkv qkv, const TcNorm norm) {
+                                                           int* __restrict__ status, const TcQkv qkv, const TcNorm norm,
+                                                           const TcUnit unit) {
     using G = TcGeometry<BN, GATED>;
     constexpr int STAGES = G::STAGES, BNO = G::BNO;
     extern __shared__ unsigned char smem_dyn[];
@@ -315,10 +324,40 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 32; ++j) u[j] = 0u;
                     }
+                    if (unit.limit > 0.f) {     // the clamped unit, with the biases of its two columns
+                        // (every lane of the warp reads the same addresses: four columns per load where they are aligned)
+                        const bool vec = unit.bias != nullptr && col0 + 32 <= N && (gate_rows & 3) == 0 &&
+                                         (((uintptr_t)unit.bias) & 15) == 0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float g = __uint_as_float(r[j]);
-                        r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * (__uint_as_float(u[j]) * inv_rms));
+                        for (int j4 = 0; j4 < 32; j4 += 4) {
+                            float bg[4] = {0.f, 0.f, 0.f, 0.f}, bu[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (vec) {
+                                const float4 a4 = __ldg(reinterpret_cast<const float4*>(unit.bias + col0 + j4));
+                                const float4 b4 = __ldg(reinterpret_cast<const float4*>(unit.bias + gate_rows + col0 + j4));
+                                bg[0] = a4.x; bg[1] = a4.y; bg[2] = a4.z; bg[3] = a4.w;
+                                bu[0] = b4.x; bu[1] = b4.y; bu[2] = b4.z; bu[3] = b4.w;
+                            } else if (unit.bias != nullptr) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (col0 + j4 + e < N) {
+                                        bg[e] = __ldg(unit.bias + col0 + j4 + e);
+                                        bu[e] = __ldg(unit.bias + gate_rows + col0 + j4 + e);
+                                    }
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int j = j4 + e;
+                                const float g = fminf(__uint_as_float(r[j]) + bg[e], unit.limit);
+                                const float v = fminf(fmaxf(__uint_as_float(u[j]) * inv_rms + bu[e], -unit.limit), unit.limit);
+                                r[j] = __float_as_uint(__fdividef(g, 1.0f + __expf(-unit.slope * g)) * (v + 1.0f));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float g = __uint_as_float(r[j]);
+                            r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * (__uint_as_float(u[j]) * inv_rms));
+                        }
                     }
                 }
                 if (!GATED && mode == TC_RELU2_BF16) {     // squared ReLU, from the float32 sums
@@ -456,7 +495,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 template <int BN, bool GATED>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int mode, int M, int N, int K,
                      long long ldc, int gate_rows, int* status, cudaStream_t stream, const TcQkv& qkv = TcQkv(),
-                     const TcNorm& norm = TcNorm()) {
+                     const TcNorm& norm = TcNorm(), const TcUnit& unit = TcUnit()) {
     using G = TcGeometry<BN, GATED>;
     auto kernel = gemm_tcgen05_kernel<BN, GATED>;
     static bool configured = false;
@@ -474,7 +513,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int 
     }
     const int ntiles = gb_ceil_div(M, TC_BM) * gb_ceil_div(N, G::BNO);
     const int grid = ntiles < sms ? ntiles : sms;   // persistent: one block per SM walks the tiles
-    cudaError_t e = gb_launch(GB_PDL_GEMM, kernel, dim3(grid), dim3(192), G::SMEM, stream, ma, mw, c, mode, M, N, K, ldc, gate_rows, status, qkv, norm);
+    cudaError_t e = gb_launch(GB_PDL_GEMM, kernel, dim3(grid), dim3(192), G::SMEM, stream, ma, mw, c, mode, M, N, K, ldc, gate_rows, status, qkv, norm, unit);
     GB_REQUIRE(e == cudaSuccess, "gb_gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
     return gb_check_launch("gb_gemm_tcgen05");
 }
@@ -574,6 +613,24 @@ GB_EXPORT int gb_gemm_tcgen05_gated(const void* a, const void* w, void* c, int M
     norm.ss_in = ss_in; norm.ss_parts = ss_parts; norm.eps = eps;
     return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), norm)
                 : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), norm);
+}
+
+// gb_gemm_tcgen05_gated with the clamped unit in the epilogue: c bfloat16 [M, inter] = g * sigmoid(slope * g) * (u + 1) with
+// g = min(a gate^T + bias[:inter], limit) and u = clamp(a up^T + bias[inter:], -limit, limit), formed from the float32
+// sums. bias (float32 [2 * inter]) may be nullptr; limit must be positive.
+GB_EXPORT int gb_gemm_tcgen05_unit(const void* a, const void* w, void* c, int M, int inter, int K, long long lda, long long ldw,
+                                   long long ldc, int* status, cudaStream_t stream, const float* bias, float limit, float slope) {
+    GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, 2 * inter, K, lda, ldw),
+               "gb_gemm_tcgen05_unit: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d I=%d K=%d)",
+               M, inter, K);
+    GB_REQUIRE(ldc >= inter && status != nullptr && limit > 0.f, "gb_gemm_tcgen05_unit: bad ldc, status or limit");
+    CUtensorMap ma, mw;
+    if (make_map(&ma, a, M, K, lda, TC_BM)) return 1;
+    const bool wide = pick_bn(M, inter, K, TC_EPI_GATED, 128) == 256;
+    if (make_map(&mw, w, 2LL * inter, K, ldw, wide ? 128 : 64)) return 1;
+    TcUnit unit = {bias, limit, slope};
+    return wide ? launch_tc<256, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), TcNorm(), unit)
+                : launch_tc<128, true>(ma, mw, c, TC_STORE_BF16, M, inter, K, ldc, inter, status, stream, TcQkv(), TcNorm(), unit);
 }
 
 // 1 if gb_gemm_tcgen05_qkv takes this head size: whole heads must tile the 128 columns of an output tile and half

@@ -392,8 +392,14 @@ __global__ void __launch_bounds__(128) sink_attention_tiles_kernel(
     const float scale2 = scale * SK_LOG2E;
     const int my_pos0 = p_lo + warp * 16 + (lane >> 2), my_pos1 = my_pos0 + 8;       // positions of this thread's two rows
     float mrow[2] = {sink2, sink2}, lrow[2] = {0.f, 0.f};                             // (a thread's share of the denominator)
+    // The bias depends on the distance alone, and a tile of 64 rows x 64 keys holds 127 distances: one logarithm per thread
+    // and tile instead of one per score. sbias[i] belongs to the distance (p_lo - kb) + i - 63, which is row - key + 63
+    // counted inside the tile; distances below zero (keys that no row of theirs sees) count as zero.
+    __shared__ float sbias[128];
+    const float* my_bias = sbias + 63 + warp * 16 + (lane >> 2) - (lane & 3) * 2;
     for (int t = 0; t < n_tiles; ++t) {
         const int kb = k_lo + t * SKT_BN, buf = t & 1;
+        if (r1) sbias[tid] = b1 * log2f(fmaf(b2, (float)max(p_lo - kb + tid - 63, 0), 1.0f));   // (read after the barrier below)
         if (t + 1 < n_tiles) {
             stage(buf ^ 1, kb + SKT_BN);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(128) sink_attention_tiles_kernel(
                     const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = e < 2 ? my_pos0 : my_pos1;
                     float v = s[j][e] * scale2;
-                    if (r1) v = fmaf(-b1, __log2f(fmaf(b2, (float)(pos - key), 1.0f)), v);
+                    if (r1) v -= my_bias[(e >> 1) * 8 - j * 8 - (e & 1)];
                     if (!whole) {
                         const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
                         v = sees ? v : -INFINITY;

@@ -66,6 +66,8 @@ _SIGNATURES = {
     "gb_gemm_tcgen05_column_tiles": [_I, _I, _I],
     "gb_gemm_tcgen05_supported": [_P, _P, _I, _I, _I, _LL, _LL],
     "gb_gemm_tcgen05_gated": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _I, _F],
+    "gb_gemm_tcgen05_unit": [_P, _P, _P, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _F, _F],
+    "gb_gemm_stream_unit": [_P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _P, _F, _F, _P, _LL, _I, _P],
     "gb_program_encode_gemm": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _I, _I],
     "gb_program_encode_gemm_qkv": [_P, _P, _LL, _P, _LL, _P, _F, _P, _LL, _P, _LL, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I,
                                    _I, _LL, _I, _P],
@@ -631,6 +633,40 @@ def gemm_tc_gated(a: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
             status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
     _call("gb_gemm_tcgen05_gated", _ptr(a), _ptr(w_gate_up), _ptr(act), M, inter, K, a.stride(0), w_gate_up.stride(0),
           act.stride(0), _ptr(status), _stream(), *(row_scale.args(M) if row_scale is not None else _NO_SCALE))
+
+
+def gemm_tc_unit(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor], limit: float, slope: float,
+                 act: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """``gemm_tc_gated`` with the clamped unit in the epilogue: act[M, I] = g * sigmoid(slope * g) * (u + 1) with
+    g = min(a gate^T + bias[:I], limit) and u = clamp(a up^T + bias[I:], -limit, limit), from the float32 sums in TMEM.
+    ``bias`` float32 [2 I] or None."""
+    _cuda(a, w_gate_up, act, bias, status)
+    M, K = a.shape
+    inter = w_gate_up.shape[0] // 2
+    assert w_gate_up.shape == (2 * inter, K) and act.shape == (M, inter) and act.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inter and bias.is_contiguous())
+    if status is None:
+        status = _tc_status.get(a.device)
+        if status is None:
+            status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
+    _call("gb_gemm_tcgen05_unit", _ptr(a), _ptr(w_gate_up), _ptr(act), M, inter, K, a.stride(0), w_gate_up.stride(0),
+          act.stride(0), _ptr(status), _stream(), _ptr(bias), float(limit), float(slope))
+
+
+def gemm_stream_unit(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor], limit: float, slope: float,
+                     act: torch.Tensor, prefetch: Optional[torch.Tensor] = None) -> None:
+    """The gated form of ``gemm_stream`` (at most 64 rows, the weights streamed once) with the clamped unit of
+    ``gemm_tc_unit`` in its epilogue; the number of units must be a multiple of 16."""
+    _cuda(a, w_gate_up, act, bias)
+    M, K = a.shape
+    inter = w_gate_up.shape[0] // 2
+    assert w_gate_up.shape == (2 * inter, K) and act.shape == (M, inter) and act.dtype == torch.bfloat16
+    assert a.dtype == torch.bfloat16 and a.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inter and bias.is_contiguous())
+    x, ldx, xres, ldr, gain, eps = _stream_input(a, None)
+    _call("gb_gemm_stream_unit", x, ldx, xres, ldr, gain, eps, _ptr(w_gate_up), w_gate_up.stride(0), _ptr(act), act.stride(0),
+          M, inter, K, _ptr(bias), float(limit), float(slope), *_prefetch_args(prefetch), 1 if USE_PDL else 0, _stream())
 
 
 def attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,

@@ -19,6 +19,14 @@ over operands that rotate through more memory than L2 holds.
                                                                          window; the grouped experts' products beside a dense product of
                                                                          as many multiply-adds; minGRU beside the delta rule; the streams'
                                                                          row kernel beside RMSNorm
+    python -m glassbox_b200.microbench tagenex                           Tagenex's kernels, each beside its like kernel: sink attention
+                                                                         with a distance bias and a gate (window 1024) beside
+                                                                         grouped-query attention with the same window; q/k norm + value
+                                                                         mixing + cache write beside rotation + cache write; the branch
+                                                                         norm into the residual beside RMSNorm; the clamped gated unit in
+                                                                         a product's epilogue beside SwiGLU in the same product; the
+                                                                         routed clamped experts beside a dense product of as many
+                                                                         multiply-adds; the router
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -392,6 +400,153 @@ def bench_lonorax() -> None:
     kernels.check_status(status)
 
 
+def bench_tagenex() -> None:
+    """Each kernel of the Tagenex path beside the like kernel of the Llama path, at the sizes of the width-1024 and width-2048
+    models that ``bench.py --workload tagenex`` runs."""
+    from .parts.rope import rotary_table
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ps, hd, window, t_len = 16, 64, 1024, 2048
+    for H, G in ((16, 4), (32, 8)):
+        per = t_len // ps
+        kc = torch.randn(per + 2, G, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        tables = torch.arange(per, dtype=torch.int32, device=DEV).view(1, per).contiguous()
+        first = torch.tensor([0, t_len], dtype=torch.int32, device=DEV)
+        start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        q = torch.randn(t_len, H * hd, device=DEV).bfloat16()
+        o = torch.empty_like(q)
+        r1, r2, sink = torch.full((H,), 0.5, device=DEV), torch.full((H,), 0.3, device=DEV), torch.zeros(H, device=DEV)
+        gate = torch.randn(t_len, H, device=DEV)
+        own = dict(r1=r1, r2=r2, sink=sink, heads=H, kv_heads=G, dim=hd, vdim=hd, page_size=ps, scale=hd ** -0.5, window=window,
+                   status=status)
+        seen = sum(min(p + 1, window) for p in range(t_len))
+        fl = 2.0 * seen * H * (hd + hd)
+        t = graph_time(lambda: kernels.sink_attention_tiles(q, o, kc, vc, tables, first, start, t_len, gate=gate, **own), reps=6)
+        print(f"sink_attention prompt heads {H}/{G} x {hd}, window {window}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
+            t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, H, G, hd, ps, hd ** -0.5, window, status), reps=6)
+            print(f"   grouped-query prompt ({name}) the same heads and window: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        # q/k norm, value mixing and the cache write from the float32 sums, beside rotation + cache write from bfloat16 sums
+        for n in (t_len, 8):
+            cols = (H + 2 * G) * hd
+            proj = torch.randn(n, cols, device=DEV)
+            pos = torch.arange(n, dtype=torch.int32, device=DEV)
+            qn, kn = torch.ones(hd, device=DEV), torch.ones(hd, device=DEV)
+            src, lam = torch.randn(n, G * hd, device=DEV), torch.full((), 0.4, device=DEV)
+            qo = torch.empty(n, H * hd, device=DEV).bfloat16()
+            t = graph_time(lambda: kernels.qk_norm_rope_write(proj, qn, kn, None, pos, pos, qo, kc, vc, H, G, hd, hd, 0, 1e-6, ps, True,
+                                                              status, values_in=src, value_mix=lam))
+            nbytes = n * (cols * 4 + G * hd * 4 + cols * 2)
+            print(f"q/k norm + value mix + cache write heads {H}/{G}, {n:4d} rows: {t:6.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            qkv = torch.randn(n, cols, device=DEV).bfloat16()
+            rope = rotary_table(10000.0, hd, 8192).to(DEV)
+            t = graph_time(lambda: kernels.rope_kv_write(qkv, rope, pos, pos, kc, vc, H, G, hd, hd, ps, True, status))
+            print(f"   rotation + cache write, {n:4d} rows: {t:6.1f} us {n * cols * 2 * 2 / t / 1e3:6.0f} GB/s", flush=True)
+        ctx = 4096
+        for m in (1, 8, 64):
+            per = ctx // ps
+            kc = torch.randn(m * per + 4, G, ps, hd, device=DEV).bfloat16()
+            vc = torch.randn_like(kc)
+            tables = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+            row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+            pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+            q = torch.randn(m, H * hd, device=DEV).bfloat16()
+            o = torch.empty_like(q)
+            gate = torch.randn(m, H, device=DEV)
+            nbytes = m * window * G * hd * 2 * 2
+            t = graph_time(lambda: kernels.sink_attention_decode(q, o, kc, vc, tables, row_seq, pos, gate=gate, **own))
+            print(f"sink_attention decode heads {H}/{G} x {hd} batch {m:3d} window {window}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            sp, block_keys, warps = kernels.decode_mma_plan(m, G, hd, window)
+            pa = torch.empty(m * H * warps * sp * hd, device=DEV)
+            pm = torch.empty(m * H * warps * sp * 2, device=DEV)
+            cn = torch.zeros(m * G, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, H, G, hd, ps, hd ** -0.5, window,
+                                                                sp, pa, pm, cn, status, block_keys, warps))
+            print(f"   grouped-query decode the same heads and window: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    # the branch norm into the residual (reads branch and residual, writes the residual and its bfloat16 copy) beside RMSNorm
+    for d in (1024, 2048):
+        for n in (2048, 8):
+            y, x, w = torch.randn(n, d, device=DEV), torch.randn(n, d, device=DEV), torch.ones(d, device=DEV)
+            h = torch.empty(n, d, device=DEV).bfloat16()
+            t = graph_time(lambda: kernels.rmsnorm_add(y, w, x, 1e-6, copy=h))
+            print(f"branch norm into the residual {d}, {n:4d} rows: {t:6.1f} us {n * d * 14 / t / 1e3:6.0f} GB/s", flush=True)
+            t = graph_time(lambda: kernels.rmsnorm(x, w, h, 1e-6))
+            print(f"   RMSNorm {d}, {n:4d} rows: {t:6.1f} us {n * d * 6 / t / 1e3:6.0f} GB/s", flush=True)
+    # the dense feed-forward's first half with the clamped unit in the epilogue, beside the same product with SwiGLU
+    for d, ff in ((1024, 4096), (2048, 8192)):
+        for n in (2048, 64, 8):
+            h = (torch.randn(n, d, device=DEV) * 0.5).bfloat16()
+            ws = _rotating(2 * ff, d)
+            bias = torch.randn(2 * ff, device=DEV) * 0.1
+            act = torch.empty(n, ff, device=DEV).bfloat16()
+            turn = [0]
+
+            def unit():
+                turn[0] += 1
+                w = ws[turn[0] % len(ws)]
+                (kernels.gemm_tc_unit(h, w, bias, 7.0, 1.702, act, status) if n > 64 else kernels.gemm_stream_unit(h, w, bias, 7.0, 1.702, act))
+
+            def swiglu():
+                turn[0] += 1
+                w = ws[turn[0] % len(ws)]
+                (kernels.gemm_tc_gated(h, w, act, status) if n > 64 else kernels.gemm_stream(h, w, act, gated=True))
+            fl, nb = 2.0 * n * 2 * ff * d, 2 * ff * d * 2
+            for name, fn in (("clamped unit", unit), ("   SwiGLU", swiglu)):
+                t = graph_time(fn, reps=6)
+                print(f"{name} in the epilogue of {d} -> 2 x {ff}, {n:4d} rows: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s {nb / t / 1e3:6.0f} GB/s", flush=True)
+    # the router and the routed clamped experts: 16 experts, four per token, beside a dense feed-forward of as many multiply-adds
+    for d, ff in ((1024, 1024), (2048, 2048)):
+        E, top = 16, 4
+        for n in (2048, 64, 8):
+            h = (torch.randn(n, d, device=DEV) * 0.5).bfloat16()
+            wr, br = torch.randn(E, d, device=DEV) * 0.05, torch.zeros(E, device=DEV)
+            positions = torch.arange(n, dtype=torch.int32, device=DEV)
+            choice = torch.empty(n, top, dtype=torch.int32, device=DEV)
+            weight = torch.empty(n, top, device=DEV)
+            t = graph_time(lambda: kernels.moe_route(h, wr, None, None, positions, top, 1, 1, 1.0, choice, weight, None, router_bias=br,
+                                                     softmax_chosen=True))
+            print(f"router {E} experts, {top} per token, width {d}, {n:4d} rows: {t:6.1f} us {(n * d * 2 + E * d * 4) / t / 1e3:6.0f} GB/s", flush=True)
+            ups = [(torch.randn(E * 2 * ff, d, device=DEV) * 0.03).bfloat16() for _ in range(3)]
+            downs = [(torch.randn(E * d, ff, device=DEV) * 0.03).bfloat16() for _ in range(3)]
+            pair = torch.empty(n, top * d, device=DEV)
+            turn = [0]
+            fl = 2.0 * n * top * 3 * d * ff
+            if n > 16:
+                tabs = torch.zeros(2 * (E + 1) + n * top, dtype=torch.int32, device=DEV)
+                act = torch.empty(n, top * ff, device=DEV).bfloat16()
+
+                def fn():
+                    turn[0] += 1
+                    kernels.moe_experts_grouped(h, ups[turn[0] % 3], downs[turn[0] % 3], E, choice, positions, tabs, act, pair, unit=(7.0, 1.702))
+            else:
+                act = torch.empty(n, top * ff, device=DEV)
+
+                def fn():
+                    turn[0] += 1
+                    kernels.moe_expert_halves(h, ups[turn[0] % 3], downs[turn[0] % 3], E, choice, positions, act, pair, unit=(7.0, 1.702))
+            t = graph_time(fn, reps=6)
+            used = int(choice.unique().numel()) * 3 * d * ff * 2       # bytes of the experts that any row chose
+            print(f"routed clamped experts {E} x ({d} -> 2 x {ff} -> {d}), {top} per token, {n:4d} rows: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s "
+                  f"{used / t / 1e3:6.0f} GB/s of chosen weights", flush=True)
+            dff = top * ff
+            w1, w2 = _rotating(2 * dff, d), _rotating(d, dff)
+            a1 = torch.empty(n, dff, device=DEV).bfloat16()
+            out = torch.empty(n, d, device=DEV)
+
+            def dense():
+                turn[0] += 1
+                if n > 64:
+                    kernels.gemm_tc_gated(h, w1[turn[0] % len(w1)], a1, status)
+                    kernels.gemm_tc(a1, w2[turn[0] % len(w2)], out, False, status)
+                else:
+                    kernels.gemm_stream(h, w1[turn[0] % len(w1)], a1, gated=True)
+                    kernels.gemm_stream(a1, w2[turn[0] % len(w2)], out)
+            t = graph_time(dense, reps=6)
+            print(f"   dense SwiGLU feed-forward {d} -> 2 x {dff} -> {d} (as many multiply-adds), {n:4d} rows: {t:7.1f} us "
+                  f"{fl / t / 1e6:6.1f} TFLOP/s {3 * d * dff * 2 / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
 def bench_float32() -> None:
     """The kernels of the true 32-bit path at SmolLM2-135M shapes: FMA products for a 2,048-token prompt and for 8
     decoded rows, split-key decode attention and one-warp-per-row attention over a float32 cache."""
@@ -574,7 +729,7 @@ def bench_layer_gemms(rows) -> None:
     kernels.check_status(st)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule", "lonorax")
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule", "lonorax", "tagenex")
 
 
 def main(argv) -> int:
@@ -610,6 +765,8 @@ def main(argv) -> int:
         bench_delta_rule()
     elif argv[0] == "lonorax":
         bench_lonorax()
+    elif argv[0] == "tagenex":
+        bench_tagenex()
     else:
         bench_attention_prefill()
     return 0

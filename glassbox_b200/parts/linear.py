@@ -141,4 +141,15 @@ def clamped_glu_linear(ctx, a, w_gate_up: torch.Tensor, bias, limit: float, slop
     """act = g * sigmoid(slope * g) * (u + 1) with g = min(a Wgate^T + b_gate, limit), u = clamp(a Wup^T + b_up, -limit,
     limit) in one kernel (the unit in the product's epilogue, from the float32 sums) when a kernel with that epilogue takes
     the operands; returns False (and does nothing) otherwise, and the caller runs the product and the unit separately."""
+    if isinstance(a, DeferredNorm) or not (a.dtype == w_gate_up.dtype == act.dtype == torch.bfloat16):
+        return False
+    inter = w_gate_up.shape[0] // 2
+    tiles = kernels.gemm_tc_supported(a, w_gate_up, act)
+    wide = tiles and _tile_kernel_wins(a.shape[0], w_gate_up)
+    if not wide and kernels.gemm_stream_supported(a, w_gate_up) and inter % 16 == 0:
+        kernels.gemm_stream_unit(a, w_gate_up, bias, limit, slope, act, prefetch=weights_ahead(ctx, w_gate_up))
+        return True
+    if wide or (tiles and a.shape[0] > kernels.STREAM_MAX_ROWS):
+        kernels.gemm_tc_unit(a, w_gate_up, bias, limit, slope, act, ctx.status)
+        return True
     return False

@@ -212,6 +212,36 @@ def test_clamped_gated_unit(dtype, n, ff, limit):
         plain.gated_unit(np.array(1.0), np.array(1.0), 1.0)
 
 
+@pytest.mark.parametrize("n, ff, d, limit", [(1, 64, 128, 2.0), (8, 48, 72, 0.75), (64, 256, 128, 7.0), (65, 64, 128, 1.0),
+                                            (300, 136, 64, 1.5), (2048, 512, 256, 3.0)])
+def test_clamped_gated_unit_in_a_products_epilogue(n, ff, d, limit):
+    """The two products of a dense feed-forward's first half with the unit formed from their float32 sums, in the kernel for
+    few rows (the weights streamed once) and in the tile kernel, with and without biases."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(n + ff)
+    bf = lambda a: _f32(a).to(torch.bfloat16)
+    h, w, b = bf(rng.standard_normal((n, d))), bf(rng.standard_normal((2 * ff, d)) * 2.0 * limit / np.sqrt(d)), rng.standard_normal(2 * ff)
+    z = h.float().cpu().numpy().astype(np.float64) @ w.float().cpu().numpy().astype(np.float64).T
+    ran = 0
+    for bias in (None, b):
+        zz = z + (_f32(bias).cpu().numpy().astype(np.float64) if bias is not None else 0.0)
+        want = plain.gated_unit(zz[:, :ff], zz[:, ff:], limit)
+        bias_dev = _f32(bias) if bias is not None else None
+        if kernels.gemm_stream_supported(h, w) and ff % 16 == 0:
+            act = torch.zeros((n, ff), dtype=torch.bfloat16, device=DEV)
+            kernels.gemm_stream_unit(h, w, bias_dev, limit, plain.SLOPE, act)
+            np.testing.assert_allclose(act.float().cpu().numpy(), want, atol=1e-2 * max(1.0, limit * limit), rtol=1e-2)
+            ran += 1
+        act = torch.zeros((n, ff), dtype=torch.bfloat16, device=DEV)
+        if kernels.gemm_tc_supported(h, w, act):
+            status = _status()
+            kernels.gemm_tc_unit(h, w, bias_dev, limit, plain.SLOPE, act, status)
+            assert int(status.item()) == 0
+            np.testing.assert_allclose(act.float().cpu().numpy(), want, atol=1e-2 * max(1.0, limit * limit), rtol=1e-2)
+            ran += 1
+    assert ran >= 2
+
+
 @pytest.mark.parametrize("E, top, d", [(6, 2, 56), (12, 3, 128), (5, 1, 33), (1, 1, 32), (8, 8, 40), (64, 5, 72)])
 @pytest.mark.parametrize("n", [9, 300])                        # (300: the form that takes several rows per block)
 def test_router_softmax_over_the_chosen(E, top, d, n):
