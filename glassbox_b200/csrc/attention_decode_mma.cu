@@ -22,13 +22,22 @@
 // counters int32 [rows * kv heads], zero on entry and left zero.
 #include "attention_decode_mma_body.cuh"
 
-template <int HD, int BK, int NW, bool CLUSTER>
+template <int HD, int BK, int NW, bool CLUSTER, bool SINK = false>
 __global__ void __launch_bounds__(NW * 32) attention_decode_mma_kernel(const DecodeAttnArgs a) {
     __shared__ DecodeAttnSmem sm;
     extern __shared__ __align__(16) float cluster_part[];   // CLUSTER: the first block's copy receives every warp's partial result
     GbPdlSync sync;
-    attention_decode_mma_body<HD, BK, GbPdlSync, NW, CLUSTER>(a, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, sm, sync, cluster_part);
+    attention_decode_mma_body<HD, BK, GbPdlSync, NW, CLUSTER, SINK>(a, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, sm, sync, cluster_part);
 }
+
+// What the SINK instantiations read beside the common arguments (see DecodeAttnArgs); all nullptr: the plain kernel runs.
+struct DecodeSinkTerms {
+    const float* r1;
+    const float* r2;
+    const float* sink;
+    const float* gate;
+    long long ld_gate;
+};
 
 // The merge runs inside a thread-block cluster in the variant for large batches (16 keys per iteration: small
 // blocks, several per SM), when the splits of a (row, kv head) fit one cluster (at most 8 blocks) and their partial
@@ -38,12 +47,12 @@ __global__ void __launch_bounds__(NW * 32) attention_decode_mma_kernel(const Dec
 // cluster's barrier is no faster than the counter (11.2 -> 12.0 us).
 constexpr int MMA_CLUSTER_SMEM_MAX = 96 * 1024;
 
-template <int HD, int BK, int NW>
+template <int HD, int BK, int NW, bool SINK = false>
 static int launch_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
                       const void* vcache, const int* block_tables, int max_pages, const int* row_seq,
                       const int* positions, int n, int nh, int nkv, int page_size, long long num_pages, float scale,
                       int window, int splits, float* part_acc, float* part_ml, int* counters, int* status, int pdl,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const DecodeSinkTerms& terms = DecodeSinkTerms()) {
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
     DecodeAttnArgs a = {};
@@ -52,6 +61,7 @@ static int launch_mma(const void* q, long long q_stride, void* out, long long ou
     a.max_pages = max_pages; a.row_seq = row_seq; a.positions = positions; a.nh = nh; a.nkv = nkv; a.page_size = page_size;
     a.page_shift = page_shift; a.num_pages = num_pages; a.scale = scale; a.window = window; a.splits = splits;
     a.part_acc = part_acc; a.part_ml = part_ml; a.counters = counters; a.status = status; a.n = n; a.hd = HD; a.block_keys = BK;
+    a.r1 = terms.r1; a.r2 = terms.r2; a.sink = terms.sink; a.gate = terms.gate; a.ld_gate = terms.ld_gate;
     a.late_release = 1;   // (135M decode step at batch 1: 0.646 -> 0.630 ms; no difference at batch 64)
     const int group = nh / nkv;
     const int cluster_bytes = decode_attn_cluster_floats<HD>(group, splits, NW) * (int)sizeof(float);
@@ -71,7 +81,7 @@ static int launch_mma(const void* q, long long q_stride, void* out, long long ou
     if (in_cluster) {
         static int configured = 0;
         if (cluster_bytes > configured) {
-            e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, BK, NW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_CLUSTER_SMEM_MAX);
+            e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, BK, NW, true, SINK>, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_CLUSTER_SMEM_MAX);
             GB_REQUIRE(e == cudaSuccess, "gb_attention_decode_mma: %d bytes of shared memory refused: %s", MMA_CLUSTER_SMEM_MAX, cudaGetErrorString(e));
             configured = MMA_CLUSTER_SMEM_MAX;
         }
@@ -83,11 +93,11 @@ static int launch_mma(const void* q, long long q_stride, void* out, long long ou
         cfg.dynamicSmemBytes = cluster_bytes;
         cfg.attrs = attr;
         cfg.numAttrs = na;
-        e = cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, BK, NW, true>, a);
+        e = cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, BK, NW, true, SINK>, a);
     } else {
         cfg.attrs = attr;
         cfg.numAttrs = na;
-        e = cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, BK, NW, false>, a);
+        e = cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, BK, NW, false, SINK>, a);
     }
     if (e != cudaSuccess) {
         gb_set_error("gb_attention_decode_mma: launch failed: %s", cudaGetErrorString(e));
@@ -107,12 +117,13 @@ GB_EXPORT int gb_attention_decode_mma_supported(int nh, int nkv, int hd) {
 // metadata until the predecessor has finished, and releases its own successor at once. block_keys
 // (0 = default) picks the variant that takes 16 keys per warp iteration where one is built (head
 // size 64): fewer registers, more blocks per SM, which pays when the batch alone fills the GPU.
-GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, void* out, long long out_stride,
-                                          const void* kcache, const void* vcache, const int* block_tables,
-                                          int max_pages, const int* row_seq, const int* positions, int n, int nh,
-                                          int nkv, int hd, int page_size, long long num_pages, float scale, int window,
-                                          int splits, float* part_acc, float* part_ml, int* counters, int* status,
-                                          int pdl, int block_keys, int warps, cudaStream_t stream) {
+template <bool SINK>
+static int decode_mma_dispatch(const void* q, long long q_stride, void* out, long long out_stride,
+                               const void* kcache, const void* vcache, const int* block_tables,
+                               int max_pages, const int* row_seq, const int* positions, int n, int nh,
+                               int nkv, int hd, int page_size, long long num_pages, float scale, int window,
+                               int splits, float* part_acc, float* part_ml, int* counters, int* status,
+                               int pdl, int block_keys, int warps, cudaStream_t stream, const DecodeSinkTerms& terms) {
     GB_REQUIRE(gb_attention_decode_mma_supported(nh, nkv, hd),
                "gb_attention_decode_mma: head size %d with %d heads per kv head is not built (16/32/64/128, <= 16)", hd,
                nkv > 0 ? nh / nkv : 0);
@@ -127,9 +138,9 @@ GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, voi
     if (n == 0) return 0;
 #define GB_MMA(HH, BB) GB_MMAW(HH, BB, 4)
 #define GB_MMAW(HH, BB, WW)                                                                                        \
-    return launch_mma<HH, BB, WW>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq, positions, \
+    return launch_mma<HH, BB, WW, SINK>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq, positions, \
                               n, nh, nkv, page_size, num_pages, scale, window, splits, part_acc, part_ml, counters,       \
-                              status, pdl, stream);
+                              status, pdl, stream, terms);
     if (hd == 16) { GB_MMA(16, 32) }
     if (hd == 32) { GB_MMA(32, 32) }
     if (hd == 64) {
@@ -141,6 +152,35 @@ GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, voi
     GB_MMA(128, 16)
 #undef GB_MMA
 #undef GB_MMAW
+}
+
+GB_EXPORT int gb_attention_decode_mma_pdl(const void* q, long long q_stride, void* out, long long out_stride,
+                                          const void* kcache, const void* vcache, const int* block_tables,
+                                          int max_pages, const int* row_seq, const int* positions, int n, int nh,
+                                          int nkv, int hd, int page_size, long long num_pages, float scale, int window,
+                                          int splits, float* part_acc, float* part_ml, int* counters, int* status,
+                                          int pdl, int block_keys, int warps, cudaStream_t stream) {
+    return decode_mma_dispatch<false>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq, positions, n, nh,
+                                      nkv, hd, page_size, num_pages, scale, window, splits, part_acc, part_ml, counters, status, pdl,
+                                      block_keys, warps, stream, DecodeSinkTerms());
+}
+
+// gb_attention_decode_mma_pdl for a softmax with a distance bias, a sink and an output gate: the score of a key `dist`
+// tokens back loses r1[head] * ln(1 + r2[head] * dist) (r1 and r2 both or neither), the denominator also holds
+// exp(sink[head]), and the head's output is multiplied by sigmoid(gate[row * ld_gate + head]). Each term may be nullptr.
+GB_EXPORT int gb_attention_decode_mma_sink(const void* q, long long q_stride, void* out, long long out_stride,
+                                           const void* kcache, const void* vcache, const int* block_tables,
+                                           int max_pages, const int* row_seq, const int* positions, int n, int nh,
+                                           int nkv, int hd, int page_size, long long num_pages, float scale, int window,
+                                           int splits, float* part_acc, float* part_ml, int* counters, int* status,
+                                           int pdl, int block_keys, int warps, const float* r1, const float* r2,
+                                           const float* sink, const float* gate, long long ld_gate, cudaStream_t stream) {
+    GB_REQUIRE((r1 == nullptr) == (r2 == nullptr), "gb_attention_decode_mma_sink: the distance bias needs r1 and r2");
+    GB_REQUIRE(gate == nullptr || ld_gate >= nh, "gb_attention_decode_mma_sink: rows of gate logits are too short");
+    DecodeSinkTerms terms = {r1, r2, sink, gate, ld_gate};
+    return decode_mma_dispatch<true>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, row_seq, positions, n, nh,
+                                     nkv, hd, page_size, num_pages, scale, window, splits, part_acc, part_ml, counters, status, pdl,
+                                     block_keys, warps, stream, terms);
 }
 
 GB_EXPORT int gb_attention_decode_mma(const void* q, long long q_stride, void* out, long long out_stride,

@@ -29,6 +29,14 @@ struct DecodeAttnArgs {
     int n;           // rows (used by the persistent kernel to count its virtual blocks)
     int hd, block_keys;
     int late_release;   // let the next kernel in the stream go only after this one's own wait (else at its start)
+    // Read only by the SINK instantiations (each may be nullptr): the score of a key `dist` tokens back loses
+    // r1[head] * ln(1 + r2[head] * dist); the softmax's denominator also holds exp(sink[head]), which has no key and
+    // no value; the head's output is multiplied by sigmoid(gate[row * ld_gate + head]) (float32 logits).
+    const float* r1;
+    const float* r2;
+    const float* sink;
+    const float* gate;
+    long long ld_gate;
 };
 
 constexpr float MMA_NEG_BIG = -1.0e30f;
@@ -104,7 +112,7 @@ __host__ __device__ constexpr int decode_attn_cluster_floats(int group, int spli
 // barrier, and the first block merges from its own shared memory: no trip through global memory, no counter, no
 // second pass over what other blocks wrote. Otherwise the partial results go through `part_acc` / `part_ml` and the
 // block that arrives last at `counters` merges them.
-template <int HD, int BK, class Sync, int NW = 4, bool CLUSTER = false>
+template <int HD, int BK, class Sync, int NW = 4, bool CLUSTER = false, bool SINK = false>
 __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& a, const int split, const int kvh, const int row,
                                                           DecodeAttnSmem& sm, Sync& sync, float* cluster_part = nullptr) {
     constexpr int NTHREADS = NW * 32;
@@ -136,6 +144,23 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
     const int head0 = kvh * G;
     const int S4 = splits * NW;   // partial results per head: one per warp of every split
     int& is_last = sm.is_last;
+    // SINK: the distance bias of this thread's two heads (rows g and g + 8 of the score tile), and what a merged head's
+    // denominator and output still need: the sink's logit joins the maximum and the sum, the gate scales the result
+    float sk_b1[2] = {0.f, 0.f}, sk_b2[2] = {0.f, 0.f};
+    if constexpr (SINK) {
+        if (a.r1 != nullptr) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (g + 8 * h < G) {
+                    sk_b1[h] = a.r1[head0 + g + 8 * h];
+                    sk_b2[h] = a.r2[head0 + g + 8 * h];
+                }
+        }
+    }
+    auto sink_logit = [&](int head) { return (SINK && a.sink != nullptr) ? a.sink[head] : MMA_NEG_BIG; };
+    auto gate_factor = [&](int head) {
+        return (SINK && a.gate != nullptr) ? 1.0f / (1.0f + __expf(-a.gate[(size_t)row * a.ld_gate + head])) : 1.0f;
+    };
 
     // This kernel's own prologue (positions, block table: step metadata that no kernel writes) runs before it waits
     // for its predecessor, which wrote the queries and this step's keys and values. The next kernel in the stream is
@@ -285,7 +310,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = base + 8 * j + 2 * t + (e & 1);
-                s[j][e] = (key < k_end && key >= first) ? s[j][e] * scale : MMA_NEG_BIG;
+                float v = s[j][e] * scale;
+                if constexpr (SINK) {
+                    if (a.r1 != nullptr) v -= sk_b1[e >> 1] * logf(fmaf(sk_b2[e >> 1], (float)max(pos - key, 0), 1.0f));
+                }
+                s[j][e] = (key < k_end && key >= first) ? v : MMA_NEG_BIG;
                 mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
             }
         float corr[2];
@@ -374,15 +403,16 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             const float* ph = cluster_part + (size_t)hi * S4 * (HD + 2);
             float m = MMA_NEG_BIG;
             for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, ph[sidx * (HD + 2) + HD]);
-            m = gb_warp_max(m);
+            const float sk = sink_logit(head0 + hi);
+            m = fmaxf(gb_warp_max(m), sk);
             float l = 0.f;
             for (int sidx = lane; sidx < S4; sidx += 32) {
                 const float w = __expf(ph[sidx * (HD + 2) + HD] - m);
                 weights[hi * S4 + sidx] = w;
                 l = fmaf(ph[sidx * (HD + 2) + HD + 1], w, l);
             }
-            l = gb_warp_sum(l);
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            l = gb_warp_sum(l) + (SINK ? __expf(sk - m) : 0.f);
+            const float inv = (l > 0.f ? 1.0f / l : 0.f) * gate_factor(head0 + hi);
             __syncwarp();
             for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }
@@ -446,10 +476,11 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             const float2* ml = reinterpret_cast<const float2*>(part_ml + ((size_t)row * nh + head0 + hi) * S4 * 2);
             const float2 p0 = lane < S4 ? __ldcg(ml + lane) : make_float2(MMA_NEG_BIG, 0.f);
             const float2 p1 = lane + 32 < S4 ? __ldcg(ml + lane + 32) : make_float2(MMA_NEG_BIG, 0.f);
-            const float m = gb_warp_max(fmaxf(p0.x, p1.x));
+            const float sk = sink_logit(head0 + hi);
+            const float m = fmaxf(gb_warp_max(fmaxf(p0.x, p1.x)), sk);
             const float w0 = __expf(p0.x - m), w1 = __expf(p1.x - m);
-            const float l = gb_warp_sum(fmaf(p0.y, w0, p1.y * w1));
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float l = gb_warp_sum(fmaf(p0.y, w0, p1.y * w1)) + (SINK ? __expf(sk - m) : 0.f);
+            const float inv = (l > 0.f ? 1.0f / l : 0.f) * gate_factor(head0 + hi);
             if (lane < S4) weights[hi * S4 + lane] = w0 * inv;
             if (lane + 32 < S4) weights[hi * S4 + lane + 32] = w1 * inv;
         }
@@ -471,15 +502,16 @@ __device__ __forceinline__ void attention_decode_mma_body(const DecodeAttnArgs& 
             const float* ml = part_ml + ((size_t)row * nh + head0 + h0 + hi) * S4 * 2;
             float m = MMA_NEG_BIG;
             for (int sidx = lane; sidx < S4; sidx += 32) m = fmaxf(m, __ldcg(ml + 2 * sidx));
-            m = gb_warp_max(m);
+            const float sk = sink_logit(head0 + h0 + hi);
+            m = fmaxf(gb_warp_max(m), sk);
             float l = 0.f;
             for (int sidx = lane; sidx < S4; sidx += 32) {
                 const float w = __expf(__ldcg(ml + 2 * sidx) - m);
                 weights[hi * S4 + sidx] = w;
                 l = fmaf(__ldcg(ml + 2 * sidx + 1), w, l);
             }
-            l = gb_warp_sum(l);
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            l = gb_warp_sum(l) + (SINK ? __expf(sk - m) : 0.f);
+            const float inv = (l > 0.f ? 1.0f / l : 0.f) * gate_factor(head0 + h0 + hi);
             __syncwarp();
             for (int sidx = lane; sidx < S4; sidx += 32) weights[hi * S4 + sidx] *= inv;
         }

@@ -50,6 +50,8 @@ _SIGNATURES = {
                            _LL, _I, _P, _P, _LL, _I, _P],
     "gb_attention_decode_mma_pdl": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
                                     _P, _P, _I, _I, _I, _P],
+    "gb_attention_decode_mma_sink": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P,
+                                     _P, _P, _I, _I, _I, _P, _P, _P, _P, _LL, _P],
     "gb_attention_decode_mma": [_P, _LL, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _P, _P, _P,
                                 _P, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
@@ -776,10 +778,12 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
                          block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int,
                          hd: int, page_size: int, scale: float, window: Optional[int], splits: int,
                          part_acc: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
-                         status: torch.Tensor, block_keys: int = 0, warps: int = 4) -> None:
+                         status: torch.Tensor, block_keys: int = 0, warps: int = 4, sink_terms=None) -> None:
     """bfloat16 split-key decode attention on the tensor cores. Scratch: part_acc float32
     [n, nh, warps*splits, hd], part_ml float32 [n, nh, warps*splits, 2], counters int32 [n*nkv], zero on entry
-    and left zero. ``warps`` per block: 4, or 8 (head size 64)."""
+    and left zero. ``warps`` per block: 4, or 8 (head size 64). ``sink_terms`` = (r1, r2, sink, gate), each a float32
+    tensor or None as in ``sink_attention_rows``: the softmax then has a distance bias, a sink in its denominator and a
+    sigmoid gate on each head's output (the kernel's instantiation for these terms; never part of a decode program)."""
     _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, part_acc, part_ml, counters, status)
     n = q.shape[0]
     assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
@@ -787,6 +791,16 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert part_acc.numel() >= n * nh * warps * splits * hd and part_ml.numel() >= n * nh * warps * splits * 2
     assert counters.numel() >= n * nkv
     prog = _program_for(status)
+    if sink_terms is not None:
+        if prog is not None:
+            prog.flush()
+        r1, r2, sink, gate = sink_terms
+        _cuda(r1, r2, sink, gate)
+        _call("gb_attention_decode_mma_sink", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+              _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, nh, nkv, hd, page_size,
+              kcache.shape[0], float(scale), int(window or 0), int(splits), _ptr(part_acc), _ptr(part_ml), _ptr(counters),
+              _ptr(status), 1 if USE_PDL else 0, int(block_keys), int(warps), *_sink_args(r1, r2, sink, gate, nh), _stream())
+        return
     if prog is not None and prog.takes_rows(n):
         if not prog.takes_attention(hd, block_keys):
             prog.flush()

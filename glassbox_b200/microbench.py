@@ -455,7 +455,16 @@ def bench_tagenex() -> None:
             gate = torch.randn(m, H, device=DEV)
             nbytes = m * window * G * hd * 2 * 2
             t = graph_time(lambda: kernels.sink_attention_decode(q, o, kc, vc, tables, row_seq, pos, gate=gate, **own))
-            print(f"sink_attention decode heads {H}/{G} x {hd} batch {m:3d} window {window}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            print(f"sink_attention decode (warps share a row's keys) heads {H}/{G} x {hd} batch {m:3d} window {window}: {t:7.1f} us "
+                  f"{nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            sp, block_keys, warps = kernels.decode_mma_plan(m, G, hd, window)
+            pa = torch.empty(m * H * warps * sp * hd, device=DEV)
+            pm = torch.empty(m * H * warps * sp * 2, device=DEV)
+            cn = torch.zeros(m * G, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, H, G, hd, ps, hd ** -0.5, window,
+                                                                sp, pa, pm, cn, status, block_keys, warps,
+                                                                sink_terms=(r1, r2, sink, gate)))
+            print(f"sink_attention decode (split keys, tensor cores) the same: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
             sp, block_keys, warps = kernels.decode_mma_plan(m, G, hd, window)
             pa = torch.empty(m * H * warps * sp * hd, device=DEV)
             pm = torch.empty(m * H * warps * sp * 2, device=DEV)

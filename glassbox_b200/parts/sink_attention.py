@@ -80,10 +80,24 @@ class SinkAttention(Mixer):
         linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
     def attend(self, ctx, q, att, cache, gate) -> None:
-        """Single decoded tokens take the kernel that shares a row's keys between the warps of a block; prompt portions in
-        bfloat16 at head sizes the tile kernel is built for run on the tensor cores; everything else (float32 portions,
-        other sizes) takes the one-warp-per-(row, head) kernel."""
+        """Single decoded tokens in bfloat16, where key and value size are equal and one the split-key tensor-core
+        kernel is built for, take that kernel's instantiation with the bias, the sink and the gate; other single tokens take
+        the kernel that shares a row's keys between the warps of a block; prompt portions in bfloat16 at head sizes the tile
+        kernel is built for run on the tensor cores; everything else (float32 portions, other sizes) takes the
+        one-warp-per-(row, head) kernel."""
         p, s = self.params, self.spec
+        if (ctx.decode_only and self.D == self.V and q.shape[0] <= 65535
+                and kernels.attention_decode_mma_supported(q.dtype, self.H, self.G, self.D, cache.page_size)):
+            n = q.shape[0]
+            reach = min(ctx.max_context, s.window) if s.window else ctx.max_context      # keys a row can see
+            splits, block_keys, warps = kernels.decode_mma_plan(n, self.G, self.D, reach)
+            part_acc = ctx.scratch("decode_part_acc", (n, self.H * warps * splits * self.D), torch.float32, grow=True)
+            part_ml = ctx.scratch("decode_part_ml", (n, self.H * warps * splits * 2), torch.float32, grow=True)
+            counters = ctx.zeros_once("decode_counters", ctx.max_rows * self.H, torch.int32)
+            kernels.attention_decode_mma(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, self.H, self.G,
+                                         self.D, cache.page_size, s.scale, s.window, splits, part_acc, part_ml, counters, ctx.status,
+                                         block_keys, warps, sink_terms=(p.get("r1"), p.get("r2"), p.get("sink"), gate))
+            return
         common = dict(r1=p.get("r1"), r2=p.get("r2"), sink=p.get("sink"), gate=gate, heads=self.H, kv_heads=self.G, dim=self.D,
                       vdim=self.V, page_size=cache.page_size, scale=s.scale, window=s.window, status=ctx.status)
         if ctx.decode_only and kernels.sink_attention_decode_supported(q.dtype, self.V):

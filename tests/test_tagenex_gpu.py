@@ -115,7 +115,8 @@ def _step_meta(step, at):
 def _run_mixer_steps(kernels, how, steps, lengths, rows_in, m, W, cache, dtype, eps, first_values=None, keep_values=False):
     """Norm, value mixing and cache write, then attention with its gate, step by step; returns the outputs per request (and
     the float32 values each row kept, if asked for). ``how``: "rows", "decode" (single-token steps take the decode kernel,
-    others the row kernel) or "tiles"."""
+    others the row kernel), "split" (single-token steps take the split-key tensor-core kernel, with another split count,
+    block size and warp count at every step) or "tiles"."""
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     window, page = (m["mask"]["size"] if "mask" in m else None), cache.page
     gate_col = (H + G) * D + G * V
@@ -153,6 +154,16 @@ def _run_mixer_steps(kernels, how, steps, lengths, rows_in, m, W, cache, dtype, 
         single = all(e is None or e[1] == 1 for e in step)
         if how == "tiles":
             kernels.sink_attention_tiles(q, out, cache.k, cache.v, tables, first, start, max(e[1] for e in step if e), gate=gate, **common)
+        elif how == "split" and single:
+            plans = [(1, 0, 4), (3, 16, 4), (2, 16, 8), (2, 0, 8), (5, 0, 4)] if D == 64 else [(1, 0, 4), (3, 0, 4), (2, 0, 4)]
+            splits, block_keys, warps = plans[sum(at) % len(plans)]
+            part_acc = torch.full((n, H * warps * splits * D), float("nan"), device=DEV)
+            part_ml = torch.full((n, H * warps * splits * 2), float("nan"), device=DEV)
+            counters = torch.zeros(n * G, dtype=torch.int32, device=DEV)
+            kernels.attention_decode_mma(q, out, cache.k, cache.v, tables, row_seq, positions, H, G, D, page, m["scale"], window,
+                                         splits, part_acc, part_ml, counters, status, block_keys, warps,
+                                         sink_terms=(common["r1"], common["r2"], common["sink"], gate))
+            assert int(counters.abs().sum().item()) == 0
         elif how == "decode" and single and kernels.sink_attention_decode_supported(dtype, V):
             kernels.sink_attention_decode(q, out, cache.k, cache.v, tables, row_seq, positions, gate=gate, **common)
         else:
@@ -362,9 +373,9 @@ def _plain_mixer(rows_in, m, W, eps, first_values=None):
 
 def _cuts(lengths, how, rng):
     """Steps that bring every request in: prompt portions of changing sizes side by side, then single tokens ("decode":
-    the last third of each request token by token, all requests in one step)."""
+    and "split": the last third of each request token by token, all requests in one step)."""
     at, steps = [0] * len(lengths), []
-    stop = [n - (n // 3 if how == "decode" else 0) for n in lengths]
+    stop = [n - (n // 3 if how in ("decode", "split") else 0) for n in lengths]
     while any(a < s for a, s in zip(at, stop)):
         step = []
         for r, n in enumerate(lengths):
@@ -383,15 +394,18 @@ def _cuts(lengths, how, rng):
 
 
 @pytest.mark.parametrize("how, dtype", [("rows", torch.float32), ("decode", torch.float32), ("rows", torch.bfloat16),
-                                        ("decode", torch.bfloat16), ("tiles", torch.bfloat16)])
+                                        ("decode", torch.bfloat16), ("tiles", torch.bfloat16), ("split", torch.bfloat16)])
 @pytest.mark.parametrize("H, G, D, V, window", [(6, 2, 20, 12, 7), (4, 4, 16, 32, 19), (8, 2, 64, 64, 33), (4, 2, 128, 64, 48),
-                                                (2, 1, 32, 128, None), (1, 1, 8, 8, 1), (3, 1, 10, 7, 5), (4, 1, 64, 32, 100)])
+                                                (2, 1, 32, 128, None), (1, 1, 8, 8, 1), (3, 1, 10, 7, 5), (4, 1, 64, 32, 100),
+                                                (16, 1, 16, 16, 20), (6, 3, 128, 128, None), (5, 5, 32, 32, 17), (12, 2, 64, 64, 60)])
 def test_sink_attention_kernels(how, dtype, H, G, D, V, window):
     """Norm, cache write and attention for three requests of unequal length whose pages lie interleaved, brought in by
     portions and single tokens, against the plain mixer over each whole request."""
     from glassbox_b200 import kernels
     if how == "tiles" and not kernels.sink_attention_tiles_supported(dtype, D, V):
         pytest.skip("no tile kernel for these head sizes")
+    if how == "split" and not (D == V and kernels.attention_decode_mma_supported(dtype, H, G, D, 16)):
+        pytest.skip("no split-key kernel for these head sizes")
     rng = np.random.default_rng(H * 1000 + D)
     m, W = _mixer_by_identity(H, G, D, V, 1.3 * D ** -0.5, window, rng)
     lengths = [131, 1, 50]
@@ -456,7 +470,7 @@ def _marked_rows(T, H, G, D, V, marked, rng):
 
 
 @pytest.mark.parametrize("how, dtype", [("rows", torch.float32), ("decode", torch.float32), ("decode", torch.bfloat16),
-                                        ("tiles", torch.bfloat16)])
+                                        ("tiles", torch.bfloat16), ("split", torch.bfloat16)])
 @pytest.mark.parametrize("window", [1, 2, 16, 19, 64, 65, None])
 def test_a_marked_key_decides_at_the_windows_edge(how, dtype, window):
     """One key whose score stands out, placed at page borders and elsewhere; queries that see it as the oldest key of
@@ -477,7 +491,7 @@ def test_a_marked_key_decides_at_the_windows_edge(how, dtype, window):
         gate = plain.logistic(rows[:, -H:])
         inside, outside = (np.abs(want[r].reshape(H, V) / gate[r][:, None]).max() for r in (i, i + 1))
         assert inside > 3.0 and outside < 2.0
-    cut = 180 if how == "decode" else T
+    cut = 180 if how in ("decode", "split") else T
     if how == "tiles":
         steps = [[(0, 70)], [(0, 2)], [(0, 58)], [(0, 64)], [(0, 136)]]
     else:
