@@ -66,7 +66,9 @@ template <int HD> struct AtGeometry {
     static constexpr int Q_BYTES = AT_BM * HD * 2, KV_BYTES = AT_BN * HD * 2;
     static constexpr int K_OFF = Q_BYTES, V_OFF = K_OFF + AT_STAGES * KV_BYTES;
     static constexpr int SH_OFF = V_OFF + AT_STAGES * KV_BYTES;
-    static constexpr int SMEM = SH_OFF + 2560;
+    // (SINK: behind the barriers and row statistics, a table of distance biases per softmax warp)
+    static constexpr int BIAS_OFF = SH_OFF + 2560, BIAS_WARP = 160;
+    static constexpr int SMEM = BIAS_OFF + 8 * BIAS_WARP * 4;
     // tensor memory: two S buffers of 128 columns, two accumulators O_g of HD columns, two P buffers of 64
     // columns (128 bfloat16 keys, two per 32-bit column)
     static constexpr int O_COL = 2 * AT_BN, P_COL = O_COL + 2 * HD;
@@ -107,13 +109,24 @@ __device__ __forceinline__ float at_exp2(float x) {
     return y;
 }
 
-template <int HD>
+// What the SINK instantiation reads beside the common arguments (each may be nullptr): the score of a key `dist` tokens
+// back loses r1[head] * ln(1 + r2[head] * dist); the softmax's denominator also holds exp(sink[head]), which has no key and
+// no value; the head's output is multiplied by sigmoid(gate[row * ld_gate + head]) (float32 logits).
+struct AtSinkTerms {
+    const float* r1;
+    const float* r2;
+    const float* sink;
+    const float* gate;
+    long long ld_gate;
+};
+
+template <int HD, bool SINK = false>
 __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long long out_stride,
     const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_first_row,
     const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int page_shift, long long num_pages,
-    float scale, int window, int* __restrict__ status) {
+    float scale, int window, int* __restrict__ status, const AtSinkTerms terms) {
     using G = AtGeometry<HD>;
     static_assert(HD == 64, "this kernel is built for head size 64");
     extern __shared__ __align__(1024) unsigned char at_smem[];
@@ -311,6 +324,22 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
         float m_run = AT_NEG_BIG, l_run = 0.f;
         bool ok = true;
         auto visible = [&](int key) { return key <= pos && (window <= 0 || key > pos - window); };
+        // SINK: the scores are brought into the base-2 domain and lose their bias before the maximum is taken, so what
+        // follows scales them by one. The bias depends on the distance alone: the 32 rows of this warp and the 128 keys of a
+        // tile are 159 distances apart, whose biases the warp writes into a table of its own per tile (five logarithms a
+        // lane in the place of 128); tb[i] belongs to the distance (first row of the warp - first key of the tile) + i - 127,
+        // distances below zero (keys that no row of theirs sees) count as zero.
+        const float slx = SINK ? 1.0f : sl2;
+        float* tb = reinterpret_cast<float*>(at_smem + G::BIAS_OFF) + (warp - 2) * G::BIAS_WARP;
+        float b1 = 0.f, b2 = 0.f;
+        bool biased = false;
+        if constexpr (SINK) {
+            biased = terms.r1 != nullptr;
+            if (biased) {
+                b1 = terms.r1[head];
+                b2 = terms.r2[head];
+            }
+        }
         for (int i = 0; i < my_tiles; ++i) {
             const int key0 = (kt_begin + 2 * i + g) * AT_BN;
             if (!mbar_wait_warp(&sh.s_full[g], i & 1, abort_flag, status)) { ok = false; break; }
@@ -320,6 +349,19 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.s_free[g]);   // the buffer may take the group's next S
+            if constexpr (SINK) {
+                if (biased) {
+                    const int base = pos_lo + q * 32 - key0 - 127;
+                    __syncwarp();                      // (the table of the tile before has been read)
+                    for (int i = lane; i < G::BIAS_WARP; i += 32) tb[i] = b1 * __log2f(fmaf(b2, (float)max(base + i, 0), 1.0f));
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < AT_BN; ++k) sv[k] = __float_as_uint(fmaf(__uint_as_float(sv[k]), sl2, -tb[lane + 127 - k]));
+                } else {
+#pragma unroll
+                    for (int k = 0; k < AT_BN; ++k) sv[k] = __float_as_uint(__uint_as_float(sv[k]) * sl2);
+                }
+            }
             // the mask matters only where the tile crosses the diagonal, the window's edge or the last key
             const bool need_mask = key0 + AT_BN - 1 > pos_lo || (window > 0 && key0 < pos_lo + AT_BM - window);
             if (need_mask) {
@@ -339,12 +381,12 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
             // O_g += P V of the group's previous tile must be complete before P is overwritten or O_g rescaled
             if (i > 0 && !mbar_wait_warp(&sh.pv_done[g], (i - 1) & 1, abort_flag, status)) { ok = false; break; }
             // raise the running maximum only when it is exceeded by more than 2^8 in the exponent
-            const bool raise = (mx - m_run) * sl2 > 8.0f;
+            const bool raise = (mx - m_run) * slx > 8.0f;
             if (i == 0) {
                 if (raise) m_run = mx;               // nothing is accumulated yet
             } else if (__any_sync(0xffffffffu, raise)) {
                 tc_fence_after();
-                const float corr = raise ? at_exp2((m_run - mx) * sl2) : 1.0f;
+                const float corr = raise ? at_exp2((m_run - mx) * slx) : 1.0f;
                 if (raise) m_run = mx;
                 l_run *= corr;
 #pragma unroll
@@ -359,8 +401,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
             // P = exp2(S * sl2 - m * sl2), two keys at a time with the packed float32 instructions. A masked key holds
             // -1e30 and comes out as exactly 0; a row that has seen no key yet (its maximum is still -1e30) must not
             // cancel that, so its offset is 0.
-            const float msl = m_run <= AT_NEG_BIG ? 0.f : m_run * sl2;
-            const float2 scale2 = make_float2(sl2, sl2), off2 = make_float2(-msl, -msl);
+            const float msl = m_run <= AT_NEG_BIG ? 0.f : m_run * slx;
+            const float2 scale2 = make_float2(slx, slx), off2 = make_float2(-msl, -msl);
             float2 l2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             uint32_t pw[AT_BN / 2];   // P_j of this row: two keys per 32-bit column of the A operand in TMEM
 #pragma unroll
@@ -392,12 +434,23 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attention_prefill_tc_kernel(
             tc_fence_after();
             const float m0 = sh.row_stat[0][0][r], l0 = sh.row_stat[0][1][r];
             const float m1 = sh.row_stat[1][0][r], l1 = sh.row_stat[1][1][r];
-            const float m = fmaxf(m0, m1);
+            float m = fmaxf(m0, m1), sink2 = AT_NEG_BIG;
+            if constexpr (SINK) {
+                if (terms.sink != nullptr) {           // the sink's logit joins the maximum and the sum, unscaled
+                    sink2 = terms.sink[head] * 1.4426950408889634f;
+                    m = fmaxf(m, sink2);
+                }
+            }
             // a group without tiles has never written its accumulator: it is not read
-            const float a0 = tiles_of[0] > 0 ? at_exp2((m0 - m) * sl2) : 0.f;
-            const float a1 = tiles_of[1] > 0 ? at_exp2((m1 - m) * sl2) : 0.f;
-            const float l = l0 * a0 + l1 * a1;
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float a0 = tiles_of[0] > 0 ? at_exp2((m0 - m) * slx) : 0.f;
+            const float a1 = tiles_of[1] > 0 ? at_exp2((m1 - m) * slx) : 0.f;
+            float l = l0 * a0 + l1 * a1;
+            if constexpr (SINK) l += at_exp2(sink2 - m);
+            float inv = l > 0.f ? 1.0f / l : 0.f;
+            if constexpr (SINK) {
+                if (terms.gate != nullptr && q_lo + r < nrows)
+                    inv *= 1.0f / (1.0f + __expf(-terms.gate[(size_t)(row0 + q_lo + r) * terms.ld_gate + head]));
+            }
             constexpr int OC = HD / 2;                 // this thread's channels: g * OC ..
             static_assert(OC == 32, "one 32-column access per accumulator");
             float o[OC];
@@ -458,11 +511,12 @@ GB_EXPORT int gb_attention_prefill_tc_supported(int nh, int nkv, int hd, int pag
 // Rows of each request are consecutive: request s owns rows seq_first_row[s] .. seq_first_row[s+1]-1, at
 // positions seq_start_pos[s] + local index. q [n_rows, >= nh*hd] and out are bfloat16 with 16-byte aligned
 // rows; kcache and vcache are one layer of the paged cache, [num_pages, nkv, page_size, hd] contiguous.
-GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, int n_rows, void* out, long long out_stride,
-                                      const void* kcache, const void* vcache, const int* block_tables, int max_pages,
-                                      const int* seq_first_row, const int* seq_start_pos, int num_seqs,
-                                      int max_rows_per_seq, int nh, int nkv, int hd, int page_size, long long num_pages,
-                                      float scale, int window, int* status, cudaStream_t stream) {
+template <bool SINK>
+static int prefill_tc_launch(const void* q, long long q_stride, int n_rows, void* out, long long out_stride,
+                             const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                             const int* seq_first_row, const int* seq_start_pos, int num_seqs,
+                             int max_rows_per_seq, int nh, int nkv, int hd, int page_size, long long num_pages,
+                             float scale, int window, int* status, cudaStream_t stream, const AtSinkTerms& terms) {
     GB_REQUIRE(gb_attention_prefill_tc_supported(nh, nkv, hd, page_size),
                "gb_attention_prefill_tc: head size %d (64) / page size %d (a power of two, 8..128) is not built", hd, page_size);
     GB_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && q_stride >= (long long)nh * hd,
@@ -478,7 +532,7 @@ GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, int n_r
     if (tc_make_map_2d(&mq, q, n_rows, (long long)nh * hd, q_stride, AT_BM, 64, "gb_attention_prefill_tc")) return 1;
     if (tc_make_map_2d(&mk, kcache, num_pages * nkv * page_size, hd, hd, page_size, 64, "gb_attention_prefill_tc")) return 1;
     if (tc_make_map_2d(&mv, vcache, num_pages * nkv * page_size, hd, hd, page_size, 64, "gb_attention_prefill_tc")) return 1;
-    auto kernel = attention_prefill_tc_kernel<64>;
+    auto kernel = attention_prefill_tc_kernel<64, SINK>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
@@ -490,7 +544,34 @@ GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, int n_r
     dim3 grid(gb_ceil_div(max_rows_per_seq, AT_BM), nh, num_seqs);
     cudaError_t e = gb_launch(GB_PDL_ATTENTION, kernel, grid, dim3(AT_WARPS * 32), G::SMEM, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride,
                               block_tables, max_pages, seq_first_row, seq_start_pos, nh, nkv, page_size, page_shift, num_pages,
-                              scale, window, status);
+                              scale, window, status, terms);
     GB_REQUIRE(e == cudaSuccess, "gb_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return gb_check_launch("gb_attention_prefill_tc");
+}
+
+GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, int n_rows, void* out, long long out_stride,
+                                      const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                                      const int* seq_first_row, const int* seq_start_pos, int num_seqs,
+                                      int max_rows_per_seq, int nh, int nkv, int hd, int page_size, long long num_pages,
+                                      float scale, int window, int* status, cudaStream_t stream) {
+    return prefill_tc_launch<false>(q, q_stride, n_rows, out, out_stride, kcache, vcache, block_tables, max_pages, seq_first_row,
+                                    seq_start_pos, num_seqs, max_rows_per_seq, nh, nkv, hd, page_size, num_pages, scale, window,
+                                    status, stream, AtSinkTerms());
+}
+
+// gb_attention_prefill_tc for a softmax with a distance bias, a sink and an output gate: the score of a key `dist` tokens
+// back loses r1[head] * ln(1 + r2[head] * dist) (r1 and r2 both or neither), the denominator also holds exp(sink[head]),
+// and the head's output is multiplied by sigmoid(gate[row * ld_gate + head]). Each term may be nullptr.
+GB_EXPORT int gb_attention_prefill_tc_sink(const void* q, long long q_stride, int n_rows, void* out, long long out_stride,
+                                           const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                                           const int* seq_first_row, const int* seq_start_pos, int num_seqs,
+                                           int max_rows_per_seq, int nh, int nkv, int hd, int page_size, long long num_pages,
+                                           float scale, int window, int* status, const float* r1, const float* r2,
+                                           const float* sink, const float* gate, long long ld_gate, cudaStream_t stream) {
+    GB_REQUIRE((r1 == nullptr) == (r2 == nullptr), "gb_attention_prefill_tc_sink: the distance bias needs r1 and r2");
+    GB_REQUIRE(gate == nullptr || ld_gate >= nh, "gb_attention_prefill_tc_sink: rows of gate logits are too short");
+    const AtSinkTerms terms = {r1, r2, sink, gate, ld_gate};
+    return prefill_tc_launch<true>(q, q_stride, n_rows, out, out_stride, kcache, vcache, block_tables, max_pages, seq_first_row,
+                                   seq_start_pos, num_seqs, max_rows_per_seq, nh, nkv, hd, page_size, num_pages, scale, window,
+                                   status, stream, terms);
 }

@@ -63,6 +63,8 @@ _SIGNATURES = {
                             _P, _I, _F],
     "gb_gemm_tcgen05_qkv_supported": [_I],
     "gb_attention_prefill_tc": [_P, _LL, _I, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_attention_prefill_tc_sink": [_P, _LL, _I, _P, _LL, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P, _P,
+                                     _P, _P, _LL, _P],
     "gb_attention_prefill_tc_supported": [_I, _I, _I, _I],
     "gb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _P, _P, _P, _P, _LL, _P, _P, _I, _F],
     "gb_gemm_tcgen05_column_tiles": [_I, _I, _I],
@@ -831,15 +833,25 @@ def attention_prefill_tc_supported(q: torch.Tensor, out: torch.Tensor, nh: int, 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                          block_tables: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
                          max_rows_per_seq: int, nh: int, nkv: int, hd: int, page_size: int, scale: float,
-                         window: Optional[int], status: torch.Tensor) -> None:
+                         window: Optional[int], status: torch.Tensor, sink_terms=None) -> None:
     """bfloat16 flash attention on tcgen05 (TMA loads from the paged cache, S and PV in tensor memory) for
-    batches whose requests bring runs of consecutive rows; arguments as ``attention_prefill``."""
+    batches whose requests bring runs of consecutive rows; arguments as ``attention_prefill``. ``sink_terms`` =
+    (r1, r2, sink, gate), each a float32 tensor or None as in ``sink_attention_rows``: the kernel's instantiation whose
+    softmax has a distance bias, a sink in its denominator and a sigmoid gate on each head's output."""
     _cuda(q, out, kcache, vcache, block_tables, seq_first_row, seq_start_pos, status)
     assert q.dtype == out.dtype == kcache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
     S = block_tables.shape[0]
     assert seq_first_row.numel() == S + 1 and seq_start_pos.numel() == S
+    if sink_terms is not None:
+        r1, r2, sink, gate = sink_terms
+        _cuda(r1, r2, sink, gate)
+        _call("gb_attention_prefill_tc_sink", _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache),
+              _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), S,
+              int(max_rows_per_seq), nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), _ptr(status),
+              *_sink_args(r1, r2, sink, gate, nh), _stream())
+        return
     _call("gb_attention_prefill_tc", _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache),
           _ptr(vcache), _ptr(block_tables), block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), S,
           int(max_rows_per_seq), nh, nkv, hd, page_size, kcache.shape[0], float(scale), int(window or 0), _ptr(status),

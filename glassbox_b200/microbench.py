@@ -422,7 +422,11 @@ def bench_tagenex() -> None:
         seen = sum(min(p + 1, window) for p in range(t_len))
         fl = 2.0 * seen * H * (hd + hd)
         t = graph_time(lambda: kernels.sink_attention_tiles(q, o, kc, vc, tables, first, start, t_len, gate=gate, **own), reps=6)
-        print(f"sink_attention prompt heads {H}/{G} x {hd}, window {window}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        print(f"sink_attention prompt (mma.sync tiles) heads {H}/{G} x {hd}, window {window}, {t_len} tokens: {t:7.1f} us "
+              f"{fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        t = graph_time(lambda: kernels.attention_prefill_tc(q, o, kc, vc, tables, first, start, t_len, H, G, hd, ps, hd ** -0.5, window,
+                                                            status, sink_terms=(r1, r2, sink, gate)), reps=6)
+        print(f"sink_attention prompt (tcgen05) the same: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
         for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
             t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, H, G, hd, ps, hd ** -0.5, window, status), reps=6)
             print(f"   grouped-query prompt ({name}) the same heads and window: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)

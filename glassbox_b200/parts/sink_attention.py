@@ -82,9 +82,10 @@ class SinkAttention(Mixer):
     def attend(self, ctx, q, att, cache, gate) -> None:
         """Single decoded tokens in bfloat16, where key and value size are equal and one the split-key tensor-core
         kernel is built for, take that kernel's instantiation with the bias, the sink and the gate; other single tokens take
-        the kernel that shares a row's keys between the warps of a block; prompt portions in bfloat16 at head sizes the tile
-        kernel is built for run on the tensor cores; everything else (float32 portions, other sizes) takes the
-        one-warp-per-(row, head) kernel."""
+        the kernel that shares a row's keys between the warps of a block; prompt portions in bfloat16 run on the tensor
+        cores: on the tcgen05 flash kernel's instantiation with the three terms where key and value size are the one it is
+        built for, else on the tile kernel at the head sizes that one is built for; everything else (float32 portions, other
+        sizes) takes the one-warp-per-(row, head) kernel."""
         p, s = self.params, self.spec
         if (ctx.decode_only and self.D == self.V and q.shape[0] <= 65535
                 and kernels.attention_decode_mma_supported(q.dtype, self.H, self.G, self.D, cache.page_size)):
@@ -102,6 +103,12 @@ class SinkAttention(Mixer):
                       vdim=self.V, page_size=cache.page_size, scale=s.scale, window=s.window, status=ctx.status)
         if ctx.decode_only and kernels.sink_attention_decode_supported(q.dtype, self.V):
             kernels.sink_attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
+            return
+        if (not ctx.decode_only and self.D == self.V
+                and kernels.attention_prefill_tc_supported(q, att, self.H, self.G, self.D, cache.page_size)):
+            kernels.attention_prefill_tc(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,
+                                         ctx.max_rows_per_seq, self.H, self.G, self.D, cache.page_size, s.scale, s.window, ctx.status,
+                                         sink_terms=(p.get("r1"), p.get("r2"), p.get("sink"), gate))
             return
         if not ctx.decode_only and kernels.sink_attention_tiles_supported(q.dtype, self.D, self.V):
             kernels.sink_attention_tiles(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,

@@ -116,7 +116,7 @@ def _run_mixer_steps(kernels, how, steps, lengths, rows_in, m, W, cache, dtype, 
     """Norm, value mixing and cache write, then attention with its gate, step by step; returns the outputs per request (and
     the float32 values each row kept, if asked for). ``how``: "rows", "decode" (single-token steps take the decode kernel,
     others the row kernel), "split" (single-token steps take the split-key tensor-core kernel, with another split count,
-    block size and warp count at every step) or "tiles"."""
+    block size and warp count at every step), "tiles" or "flash" (the tcgen05 kernel)."""
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     window, page = (m["mask"]["size"] if "mask" in m else None), cache.page
     gate_col = (H + G) * D + G * V
@@ -152,7 +152,10 @@ def _run_mixer_steps(kernels, how, steps, lengths, rows_in, m, W, cache, dtype, 
         tables = _i32([[-1] * cache.width if e is None else cache.row(e[0]) for e in step])
         gate = proj[:, gate_col:]
         single = all(e is None or e[1] == 1 for e in step)
-        if how == "tiles":
+        if how == "flash":
+            kernels.attention_prefill_tc(q, out, cache.k, cache.v, tables, first, start, max(e[1] for e in step if e), H, G, D, page,
+                                         m["scale"], window, status, sink_terms=(common["r1"], common["r2"], common["sink"], gate))
+        elif how == "tiles":
             kernels.sink_attention_tiles(q, out, cache.k, cache.v, tables, first, start, max(e[1] for e in step if e), gate=gate, **common)
         elif how == "split" and single:
             plans = [(1, 0, 4), (3, 16, 4), (2, 16, 8), (2, 0, 8), (5, 0, 4)] if D == 64 else [(1, 0, 4), (3, 0, 4), (2, 0, 4)]
@@ -394,7 +397,8 @@ def _cuts(lengths, how, rng):
 
 
 @pytest.mark.parametrize("how, dtype", [("rows", torch.float32), ("decode", torch.float32), ("rows", torch.bfloat16),
-                                        ("decode", torch.bfloat16), ("tiles", torch.bfloat16), ("split", torch.bfloat16)])
+                                        ("decode", torch.bfloat16), ("tiles", torch.bfloat16), ("split", torch.bfloat16),
+                                        ("flash", torch.bfloat16)])
 @pytest.mark.parametrize("H, G, D, V, window", [(6, 2, 20, 12, 7), (4, 4, 16, 32, 19), (8, 2, 64, 64, 33), (4, 2, 128, 64, 48),
                                                 (2, 1, 32, 128, None), (1, 1, 8, 8, 1), (3, 1, 10, 7, 5), (4, 1, 64, 32, 100),
                                                 (16, 1, 16, 16, 20), (6, 3, 128, 128, None), (5, 5, 32, 32, 17), (12, 2, 64, 64, 60)])
@@ -406,6 +410,8 @@ def test_sink_attention_kernels(how, dtype, H, G, D, V, window):
         pytest.skip("no tile kernel for these head sizes")
     if how == "split" and not (D == V and kernels.attention_decode_mma_supported(dtype, H, G, D, 16)):
         pytest.skip("no split-key kernel for these head sizes")
+    if how == "flash" and not (D == V and kernels.lib().gb_attention_prefill_tc_supported(H, G, D, 16)):
+        pytest.skip("no tcgen05 flash kernel for these head sizes")
     rng = np.random.default_rng(H * 1000 + D)
     m, W = _mixer_by_identity(H, G, D, V, 1.3 * D ** -0.5, window, rng)
     lengths = [131, 1, 50]
@@ -470,8 +476,8 @@ def _marked_rows(T, H, G, D, V, marked, rng):
 
 
 @pytest.mark.parametrize("how, dtype", [("rows", torch.float32), ("decode", torch.float32), ("decode", torch.bfloat16),
-                                        ("tiles", torch.bfloat16), ("split", torch.bfloat16)])
-@pytest.mark.parametrize("window", [1, 2, 16, 19, 64, 65, None])
+                                        ("tiles", torch.bfloat16), ("split", torch.bfloat16), ("flash", torch.bfloat16)])
+@pytest.mark.parametrize("window", [1, 2, 16, 19, 64, 65, 128, 129, None])
 def test_a_marked_key_decides_at_the_windows_edge(how, dtype, window):
     """One key whose score stands out, placed at page borders and elsewhere; queries that see it as the oldest key of
     their window and queries one token later, which must not; without a window, a marked key hundreds of tokens back. The
@@ -479,6 +485,8 @@ def test_a_marked_key_decides_at_the_windows_edge(how, dtype, window):
     from glassbox_b200 import kernels
     rng = np.random.default_rng(window or 0)
     H, G, D, V, T = 4, 2, 32, 32, 330
+    if how == "flash":                      # (built for this head size; its tiles are 128 rows by 128 keys)
+        D = V = 64
     marked = [0, 15, 16, 31, 47, 48, 100, 128, 200]
     m, W = _mixer_by_identity(H, G, D, V, 0.5, window, rng)
     W["q.norm"], W["k.norm"] = np.ones(D), np.ones(D)
@@ -492,7 +500,7 @@ def test_a_marked_key_decides_at_the_windows_edge(how, dtype, window):
         inside, outside = (np.abs(want[r].reshape(H, V) / gate[r][:, None]).max() for r in (i, i + 1))
         assert inside > 3.0 and outside < 2.0
     cut = 180 if how in ("decode", "split") else T
-    if how == "tiles":
+    if how in ("tiles", "flash"):
         steps = [[(0, 70)], [(0, 2)], [(0, 58)], [(0, 64)], [(0, 136)]]
     else:
         steps = [[(0, cut)]] if cut < T else [[(0, 33)], [(0, 150)], [(0, 147)]]
