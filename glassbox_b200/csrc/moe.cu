@@ -108,27 +108,33 @@ __device__ __forceinline__ void moe_choose(const float* score, float* choice, fl
             if (!kept[e / per]) choice[e] = -INFINITY;
         __syncwarp();
     }
+    // The chosen values wait in the row's run_score (its use above is over) and reach global memory once, at the end: a
+    // store and a load of the same address per choice would put a trip to memory into each turn of this chain.
     for (int k = 0; k < top; ++k) {
         const int e = moe_warp_argmax(choice, E, lane);
         __syncwarp();
         if (lane == 0) {
             choice_out[k] = e;                                               // -1: fewer experts could be chosen than `top`
-            weight_out[k] = e >= 0 ? score[e] * route_scale : 0.f;
+            run_score[k] = e >= 0 ? score[e] * route_scale : (softmax_chosen ? -INFINITY : 0.f);
             if (e >= 0) choice[e] = -INFINITY;
         }
         __syncwarp();
     }
-    if (softmax_chosen && lane == 0) {
-        // weight_out holds the chosen logits, the largest first: softmax over them alone
-        const float m = weight_out[0];
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const float w = choice_out[k] >= 0 ? expf(weight_out[k] - m) : 0.f;
-            weight_out[k] = w;
-            sum += w;
+    if (lane == 0) {
+        if (softmax_chosen) {
+            // run_score holds the chosen logits, the largest first: softmax over them alone
+            const float m = run_score[0];
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const float w = run_score[k] > -INFINITY ? expf(run_score[k] - m) : 0.f;
+                run_score[k] = w;
+                sum += w;
+            }
+            const float inv = 1.0f / sum;
+            for (int k = 0; k < top; ++k) weight_out[k] = run_score[k] * inv;
+        } else {
+            for (int k = 0; k < top; ++k) weight_out[k] = run_score[k];
         }
-        const float inv = 1.0f / sum;
-        for (int k = 0; k < top; ++k) weight_out[k] *= inv;
     }
 }
 
