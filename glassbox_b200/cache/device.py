@@ -13,7 +13,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import PagedKvSpec, StateSpec
+from ..parts.base import CombinedCacheSpec, PagedKvSpec, StateSpec
 
 
 @dataclass
@@ -32,6 +32,26 @@ class StateLayerView:
     state: torch.Tensor             # [max_requests, *shape]; index with ctx.seq_slots
 
 
+@dataclass
+class CombinedLayerView:
+    """The view of a cache layer that keeps pages and named states (``CombinedCacheSpec``)."""
+    paged: Optional[PagedLayerView]
+    states: Dict[str, torch.Tensor]     # name -> [max_requests, *shape]
+
+    def part(self, name: str, spec):
+        """The view that the user called ``name`` would have got had it had the cache layer to itself (``spec``: what it
+        declared)."""
+        if spec is None:
+            return None
+        if isinstance(spec, PagedKvSpec):
+            return self.paged
+        if isinstance(spec, StateSpec):
+            return StateLayerView(state=self.states[name or "state"])
+        prefix = name + "." if name else ""
+        return CombinedLayerView(self.paged if spec.paged is not None else None,
+                                 {n: self.states[prefix + n] for n, _ in spec.states})
+
+
 class DeviceCache:
     def __init__(self, layer_specs: List[object], pages_per_group, page_size: int, max_requests: int,
                  dtype: torch.dtype, device):
@@ -43,8 +63,16 @@ class DeviceCache:
         self.group_of_layer: Dict[int, int] = {}
         self.index_in_group: Dict[int, int] = {}
         members: List[List[int]] = []
-        self.state: Dict[int, torch.Tensor] = {}
+        self.state: Dict[object, torch.Tensor] = {}
+        self.combined: Dict[int, CombinedCacheSpec] = {}
         for c, spec in enumerate(layer_specs):
+            if isinstance(spec, CombinedCacheSpec):
+                self.combined[c] = spec
+                for name, st in spec.states:
+                    self.state[(c, name)] = torch.zeros((max_requests,) + tuple(st.shape), dtype=st.dtype, device=device)
+                spec = spec.paged
+                if spec is None:
+                    continue
             if isinstance(spec, PagedKvSpec):
                 if spec not in self.group_specs:
                     self.group_specs.append(spec)
@@ -84,6 +112,12 @@ class DeviceCache:
         return total
 
     def layer_view(self, cache_layer: int):
+        if cache_layer in self.combined:
+            paged = None
+            if cache_layer in self.group_of_layer:
+                g, i = self.group_of_layer[cache_layer], self.index_in_group[cache_layer]
+                paged = PagedLayerView(k=self.k[g][i], v=self.v[g][i], page_size=self.page_size, group=g)
+            return CombinedLayerView(paged, {n: self.state[(cache_layer, n)] for n, _ in self.combined[cache_layer].states})
         if cache_layer in self.group_of_layer:
             g = self.group_of_layer[cache_layer]
             i = self.index_in_group[cache_layer]

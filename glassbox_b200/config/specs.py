@@ -32,7 +32,24 @@ class RopeSpec:
     rotary_dim: int
     max_position: int
     pairing: str = "half"
+    #: None, or a ``RopeRescaleSpec``: the frequencies are stretched for contexts longer than the trained one
+    rescale: Any = None
     kind: str = "rope"
+
+
+@dataclass(frozen=True)
+class RopeRescaleSpec:
+    """Stretching of a rotation's frequencies by wavelength: with dim(t) = rotary_dim * ln(``original`` / (2 pi t)) /
+    (2 ln theta), lo = max(floor(dim(``fast``)), 0), hi = min(ceil(dim(``slow``)), rotary_dim - 1) and ramp_i =
+    clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes f_i / ``factor`` * ramp_i + f_i * (1 - ramp_i): pairs
+    that turn more than ``fast`` times within the ``original`` context keep their frequency, pairs that turn less than
+    ``slow`` times are slowed by ``factor``, the ones between are blended. Sine and cosine carry the factor
+    ``magnitude_slope`` * ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    magnitude_slope: float = 0.1
 
 
 @dataclass(frozen=True)
@@ -162,6 +179,68 @@ class SinkAttentionSpec:
 
 
 @dataclass(frozen=True)
+class TalkingAttentionSpec:
+    """Causal grouped-query softmax attention whose heads exchange their weights: after the softmax the weights of query
+    head h become sum_g ``talk``[h, g] * weight_g (a learned [heads, heads] matrix), and head h applies them to the values
+    of its own key/value head. Scores are q . k * ``scale``, then (``softcap`` not None) softcap * tanh(score / softcap).
+    ``unit_sink`` adds one to the softmax's denominator: a key of score 0 that has no value and whose share is not mixed.
+    ``bias``: q, k and v carry biases, added in the projection. ``position`` rotates the leading channels of queries and
+    keys. ``window`` as in ``GqaAttentionSpec``. ``talk`` False leaves the weights as they are."""
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: Any
+    softcap: Optional[float] = None
+    unit_sink: bool = True
+    bias: bool = True
+    talk: bool = True
+    window: Optional[int] = None
+    kind: str = "talking_attention"
+
+
+@dataclass(frozen=True)
+class DecayLinearAttentionSpec:
+    """Linear attention with one fixed decay per head: q = silu(W_q h), k = silu(W_k h) (heads x head_dim), v = silu(W_v h)
+    (heads x value_dim); per head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with a float32 state S [head_dim,
+    value_dim] per request. The heads' read-outs are RMS-normed together (``norm_eps``, a gain per channel), times
+    sigmoid(W_g h), and projected."""
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    norm_eps: float
+    kind: str = "decay_linear_attention"
+
+
+@dataclass(frozen=True)
+class HeadDeltaSpec:
+    """A gated delta-rule mixer with ONE decay per head and token: as ``ChannelDeltaSpec`` (state, convolutions, unit
+    vectors, beta, read-out norm per head), but g = exp(-exp(A_log_h) * softplus(w_a_h . x + dt_bias_h)) is one number per
+    head, decay and output gate are plain projections of the input, and the gate is silu (``gate`` "silu") or a sigmoid."""
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    gate: str = "silu"
+    kind: str = "head_delta"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input: the output is ``left_scale`` * left + ``right_scale`` * right.
+    Either may keep keys in pages, a state per request, or both."""
+    left: Any
+    right: Any
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class MinGruSpec:
     """minGRU: per channel S_t = (1 - z_t) S_(t-1) + z_t c_t with the gate z_t = sigmoid(W_z h + b_z) and the candidate c_t
     from u = W_x h + b_x (u + 1/2 where u >= 0, sigmoid(u) elsewhere), both functions of the current token alone; the
@@ -226,6 +305,14 @@ class SwiGluSpec:
 
 
 @dataclass(frozen=True)
+class GeluGluSpec:
+    """Dense gated feed-forward whose gate passes the tanh form of GELU: down(gelu_tanh(gate(x)) * up(x)) with
+    gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))."""
+    intermediate_size: int
+    kind: str = "gelu_glu"
+
+
+@dataclass(frozen=True)
 class EmbeddingSpec:
     """Token embedding: the float32 residual row of a token is its row of the table, as it is
     (crates/glassbox-core/src/model.rs:228-231). Another kind (a scaled table, a learned position added to it) is
@@ -238,6 +325,14 @@ class ScaledEmbeddingSpec:
     """Token embedding times a constant: the residual row of a token is its row of the table times ``scale``."""
     scale: float
     kind: str = "scaled_embedding"
+
+
+@dataclass(frozen=True)
+class PositionalEmbeddingSpec:
+    """Token embedding plus a learned vector per position: the residual row of a token at position p is its row of the
+    table plus row p of a second table of ``max_position`` rows (neither scaled), summed in float32."""
+    max_position: int
+    kind: str = "positional_embedding"
 
 
 @dataclass(frozen=True)
@@ -276,6 +371,14 @@ class LayerSpec:
     #: its norm and its output comes back into all of them through a learned matrix (``ModelConfig.residual_streams`` says
     #: the same number for the whole model); ``ffn`` may be None
     streams: int = 0
+    #: "hyper_connections" with ``learned_streams`` False has no stream tensors: it reads the plain sum, every stream
+    #: keeps itself and takes the branch's output once (with one stream this is the plain residual)
+    learned_streams: bool = True
+    #: every branch's output is multiplied by this before it joins the residual (arrangement "hyper_connections")
+    branch_scale: float = 1.0
+    #: taps of a causal convolution over time, per channel, on what the mixer reads: h <- h + conv(h), with the last
+    #: taps - 1 inputs kept per request (arrangement "hyper_connections"); 0: none
+    mixer_input_conv: int = 0
 
 
 @dataclass(frozen=True)

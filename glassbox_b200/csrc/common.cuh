@@ -49,6 +49,11 @@ __device__ __forceinline__ float gb_clamped_unit(float gate, float up, float lim
     return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
 }
 
+// The tanh form of GELU: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gb_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -124,7 +124,15 @@ struct ChannelDeltaArgs {
     const int* seq_slots;
     int heads, kv_heads, dk, dv, ns, tc, num_slots, write_state;
     int* status;
+    int decay_channels;     // dk: a decay per head and key channel (a, dt_bias: heads * dk); 1: one per head (a, dt_bias: heads)
+    int flags;              // CD_* below
 };
+// CD_SILU_INPUTS: q, k and v pass SiLU as they are read (a mixer without convolutions in front).
+// CD_PLAIN: linear attention with a fixed decay per head, S <- decay_h S + k v^T, o = S^T q: no beta, no correction towards
+//           the value, no unit vectors, no factor on q; `a_log` then holds the decays themselves, a, beta and dt_bias are not read.
+// CD_GATE_SILU: the decoding form's output gate is silu(gate) instead of sigmoid(gate).
+enum { CD_SILU_INPUTS = 1, CD_PLAIN = 2, CD_GATE_SILU = 4 };
+__device__ __forceinline__ float cd_silu(float v) { return v / (1.0f + expf(-v)); }
 
 template <int DPT, int NS>
 __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaArgs p) {
@@ -151,8 +159,12 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
     const int buf_floats = TC * per_token;
     // one buffer: q [TC][row_w], k [TC][row_w], g [TC][row_w], v [TC][cols], scalars [TC][4] = (beta, 1/|q| / sqrt(dk), 1/|k|, -)
     const int n_chunks = (r1 - r0 + TC - 1) / TC;
-    const float decay_rate = expf(p.a_log[head]);
-    const float q_scale = 1.0f / sqrtf((float)dk);
+    const bool plain = p.flags & CD_PLAIN, silu_in = p.flags & CD_SILU_INPUTS;
+    const float decay_rate = plain ? 0.f : expf(p.a_log[head]);
+    const float fixed_decay = plain ? p.a_log[head] : 1.f;
+    const float q_scale = plain ? 1.0f : 1.0f / sqrtf((float)dk);
+    const float corr = plain ? 0.f : 1.f;               // how much of S^T k is taken off the value
+    const int dc = p.decay_channels;
 
     auto stage = [&](int chunk) {
         float* buf = cd_smem + (size_t)(chunk & 1) * buf_floats;
@@ -164,9 +176,11 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
         // everything the chunk needs from memory is asked for before anything is used
         const int vidx = wt, vt_ = vidx >> cols_shift, vcl = vidx & (cols - 1), vcc = blockIdx.z * cols + vcl;
         float vv = 0.f, bb = 0.f;
-        if (vidx < nt * cols && vcc < dv)
+        if (vidx < nt * cols && vcc < dv) {
             vv = p.qkv[(size_t)(c0 + vt_) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + vcc];
-        if (wt < nt) bb = p.beta[(size_t)(c0 + wt) * p.ldb + head];
+            if (silu_in) vv = cd_silu(vv);
+        }
+        if (wt < nt && !plain) bb = p.beta[(size_t)(c0 + wt) * p.ldb + head];
         constexpr int U = 8;
         for (int base = wt; base < total; base += CD_STAGERS * U) {
             float qv[U], kv[U], zv[U];
@@ -180,7 +194,11 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                     const size_t row = (size_t)(c0 + t);
                     qv[u] = p.qkv[row * p.ldq + (size_t)kvh * dk + d];
                     kv[u] = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + d];
-                    zv[u] = p.a[row * p.lda + (size_t)head * dk + d] + p.dt_bias[(size_t)head * dk + d];
+                    if (!plain) {
+                        const size_t ai = (size_t)head * dc + (dc > 1 ? d : 0);
+                        zv[u] = p.a[row * p.lda + ai] + p.dt_bias[ai];
+                    }
+                    if (silu_in) { qv[u] = cd_silu(qv[u]); kv[u] = cd_silu(kv[u]); }
                 }
             }
 #pragma unroll
@@ -192,7 +210,7 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                     const float sp = zv[u] > 15.f ? zv[u] : __logf(1.0f + __expf(zv[u]));     // (padding channels: sp = 0, g = 1)
                     qs[at] = qv[u];
                     ks[at] = kv[u];
-                    gs[at] = __expf(-decay_rate * sp);
+                    gs[at] = (plain && d < dk) ? fixed_decay : __expf(-decay_rate * sp);
                 }
             }
         }
@@ -200,9 +218,10 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
         for (int idx = wt + CD_STAGERS; idx < nt * cols; idx += CD_STAGERS) {     // (more than 256 values: few splits, many columns)
             const int t = idx >> cols_shift, cl = idx & (cols - 1);
             const int cc = blockIdx.z * cols + cl;
-            vs[idx] = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
+            float val = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
+            vs[idx] = silu_in ? cd_silu(val) : val;
         }
-        if (wt < nt) sc[wt * 4] = 1.0f / (1.0f + __expf(-bb));
+        if (wt < nt) sc[wt * 4] = plain ? 1.0f : 1.0f / (1.0f + __expf(-bb));
         asm volatile("bar.sync 1, 256;" ::: "memory");         // the stagers among themselves
         const int lane = wt & 31;
         for (int t = wt >> 5; t < nt; t += CD_STAGERS / 32) {
@@ -215,8 +234,8 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
             sq = gb_warp_sum(sq);
             sk = gb_warp_sum(sk);
             if (lane == 0) {
-                sc[t * 4 + 1] = q_scale / sqrtf(sq + CD_UNIT_EPS);
-                sc[t * 4 + 2] = 1.0f / sqrtf(sk + CD_UNIT_EPS);
+                sc[t * 4 + 1] = plain ? 1.0f : q_scale / sqrtf(sq + CD_UNIT_EPS);
+                sc[t * 4 + 2] = plain ? 1.0f : 1.0f / sqrtf(sk + CD_UNIT_EPS);
             }
         }
     };
@@ -297,7 +316,7 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                     o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
                 }
                 if (o_row >= 0 && split == 0 && live) p.out[(size_t)o_row * p.heads * dv + (size_t)head * dv + col] = o_part;
-                const float u = scal.x * (vt - scal.z * sk) * scal.z;     // beta (v - S^T k), times 1/|k| for the update below
+                const float u = scal.x * (vt - corr * scal.z * sk) * scal.z;     // beta (v - S^T k), times 1/|k| for the update below
                 a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT / 4; ++i) {
@@ -334,9 +353,12 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
 GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* beta, long long ldb, const float* a, long long lda,
                                const float* dt_bias, const float* a_log, float* state, long long state_stride, float* out,
                                const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int heads,
-                               int kv_heads, int dk, int dv, int num_slots, int write_state, int* status, cudaStream_t stream) {
+                               int kv_heads, int dk, int dv, int num_slots, int write_state, int* status, int decay_channels,
+                               int flags, cudaStream_t stream) {
     GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta: heads %d must be a multiple of key heads %d",
                heads, kv_heads);
+    GB_REQUIRE(decay_channels == 1 || decay_channels == dk, "gb_channel_delta: %d decays per head (one, or one per key channel)",
+               decay_channels);
     GB_REQUIRE(dk > 0 && dk <= 1024 && dv > 0, "gb_channel_delta: a key size of %d is outside 1..1024", dk);
     if (S == 0) return 0;
     const int dpt = dk <= 128 ? 16 : 32;
@@ -348,7 +370,7 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
     if (tc > 16) tc = 16;
     if (tc < 1) tc = 1;
     ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, out, seq_first_row, seq_start_pos,
-                          seq_slots, heads, kv_heads, dk, dv, ns, tc, num_slots, write_state, status};
+                          seq_slots, heads, kv_heads, dk, dv, ns, tc, num_slots, write_state, status, decay_channels, flags};
     dim3 grid(S, heads, gb_ceil_div(dv, cols));
     const size_t smem = (size_t)2 * tc * per_token;
     bool launched = false;
@@ -474,9 +496,10 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
         }
     } else {
         if (tid < dk) {
+            const size_t ai = (size_t)head * p.decay_channels + (p.decay_channels > 1 ? tid : 0);
             qv = p.qkv[row * p.ldq + (size_t)kvh * dk + tid];
             kv = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + tid];
-            zv = p.a[row * p.lda + (size_t)head * dk + tid] + p.dt_bias[(size_t)head * dk + tid];
+            zv = p.a[row * p.lda + ai] + p.dt_bias[ai];
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -559,7 +582,8 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
     __syncthreads();
     if (tid < dv) {
         const float s = 1.0f / sqrtf((red[8] + red[9] + red[10] + red[11]) / (float)dv + eps);
-        const float sig = 1.0f / (1.0f + expf(-(FUSED ? gsm[tid] : gate[row * ldg + (size_t)head * dv + tid])));
+        const float gl = FUSED ? gsm[tid] : gate[row * ldg + (size_t)head * dv + tid];
+        const float sig = (p.flags & CD_GATE_SILU) ? cd_silu(gl) : 1.0f / (1.0f + expf(-gl));
         att[row * p.heads * dv + (size_t)head * dv + tid] = gb_from_float<T>(ovec[tid] * s * norm_w[tid] * sig);
     }
 }
@@ -577,7 +601,10 @@ GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const flo
                                       int kv_heads, int dk, int dv, int num_slots, int write_state, int* status,
                                       const float* proj, long long ldp, const float* conv_w, long long conv_state_off, int taps,
                                       int a1_at, int ra, int rg, const void* w_a2, const void* w_g2, int w_dtype,
-                                      cudaStream_t stream) {
+                                      int decay_channels, int flags, cudaStream_t stream) {
+    GB_REQUIRE((decay_channels == 1 || decay_channels == dk) && !(flags & (CD_PLAIN | CD_SILU_INPUTS)),
+               "gb_channel_delta_decode: %d decays per head, flags %d are not taken", decay_channels, flags);
+    GB_REQUIRE(proj == nullptr || decay_channels == dk, "gb_channel_delta_decode: the fused form wants a decay per key channel");
     GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta_decode: heads %d must be a multiple of "
                "key heads %d", heads, kv_heads);
     GB_REQUIRE(gb_channel_delta_decode_supported(dk, dv), "gb_channel_delta_decode: key size %d and value size %d must be at most 128", dk, dv);
@@ -586,7 +613,7 @@ GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const flo
                "gb_channel_delta_decode: the fused form takes low ranks up to %d in all", CD_MAX_LOW_RANK);
     if (S == 0) return 0;
     ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, nullptr, seq_first_row, seq_start_pos,
-                          seq_slots, heads, kv_heads, dk, dv, 0, 0, num_slots, write_state, status};
+                          seq_slots, heads, kv_heads, dk, dv, 0, 0, num_slots, write_state, status, decay_channels, flags};
     DeltaDecodeFusion f = {proj, ldp, conv_w, conv_state_off, taps, 2 * kv_heads * dk + heads * dv, a1_at, ra, rg, w_a2, w_g2};
     dim3 grid(S, heads);
 #define CDD_LAUNCH(T, TW, F) gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<T, TW, F>, grid, dim3(256), 0, stream, p, gate, ldg, \
@@ -618,4 +645,92 @@ GB_EXPORT int gb_short_conv_state(const float* x, long long ldx, float* state, l
     gb_launch(GB_PDL_ELEMENTWISE, short_conv_state_kernel, grid, dim3(256), 0, stream, x, ldx, state, state_stride, state_off,
               seq_first_row, seq_start_pos, seq_slots, S, C, taps, num_slots);
     return gb_check_launch("gb_short_conv_state");
+}
+
+// ----------------------------------------------------------------------------------------------
+// A causal convolution added to its own input: y[t, c] = x[t, c] + sum_j w[c, j] x[t - (taps-1) + j, c] along each request's
+// rows, x and y in the activation dtype, sums in float32. Inputs from before a portion's first row come from the request's
+// slot (float32, [taps-1, C] from `state_off` on, oldest first; zeros for a fresh request); afterwards the slot keeps the
+// portion's last taps-1 inputs. x and y must be different buffers (a row reads the rows before it).
+// ----------------------------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256) residual_conv_kernel(const T* __restrict__ x, const TW* __restrict__ w, T* __restrict__ y,
+                                                            const float* __restrict__ state, long long state_stride, long long state_off,
+                                                            const int* __restrict__ row_seq, const int* __restrict__ positions,
+                                                            const int* __restrict__ seq_first_row, const int* __restrict__ seq_slots,
+                                                            int n, int C, int taps, int num_slots, int* __restrict__ status) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (row >= n || ch >= C) return;
+    if (positions[row] < 0) return;
+    const int seq = row_seq[row];
+    const int r0 = seq_first_row[seq];
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= num_slots) {
+        atomicOr(status, GB_STATUS_BAD_SLOT);
+        return;
+    }
+    const float* st = state + (size_t)slot * state_stride + state_off;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = row - (taps - 1) + j;
+        const float v = src >= r0 ? gb_to_float(x[(size_t)src * C + ch]) : st[(size_t)(taps - 1 - (r0 - src)) * C + ch];
+        acc = fmaf(gb_to_float(w[(size_t)ch * taps + j]), v, acc);
+    }
+    y[(size_t)row * C + ch] = gb_from_float<T>(gb_to_float(x[(size_t)row * C + ch]) + acc);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) residual_conv_state_kernel(const T* __restrict__ x, float* __restrict__ state, long long state_stride,
+                                                                  long long state_off, const int* __restrict__ seq_first_row,
+                                                                  const int* __restrict__ seq_start_pos, const int* __restrict__ seq_slots,
+                                                                  int S, int C, int taps, int num_slots) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (seq >= S || ch >= C) return;
+    if (seq_start_pos[seq] < 0) return;
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= num_slots) return;
+    const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
+    float* st = state + (size_t)slot * state_stride + state_off;
+    const int keep = taps - 1;
+    for (int i = 0; i < keep; ++i) {      // increasing i: a kept value moves to a lower index than any still to be read
+        const int p = len - keep + i;
+        st[(size_t)i * C + ch] = p >= 0 ? gb_to_float(x[(size_t)(r0 + p) * C + ch]) : st[(size_t)(i + len) * C + ch];
+    }
+}
+
+template <typename T, typename TW>
+static int residual_conv_launch(const void* x, const void* w, void* y, float* state, long long state_stride, long long state_off,
+                                const int* row_seq, const int* positions, const int* seq_first_row, const int* seq_start_pos,
+                                const int* seq_slots, int n, int S, int C, int taps, int num_slots, int update_state, int* status,
+                                cudaStream_t stream) {
+    dim3 grid(n, gb_ceil_div(C, 256));
+    gb_launch(GB_PDL_ELEMENTWISE, residual_conv_kernel<T, TW>, grid, dim3(256), 0, stream, (const T*)x, (const TW*)w, (T*)y,
+              (const float*)state, state_stride, state_off, row_seq, positions, seq_first_row, seq_slots, n, C, taps, num_slots, status);
+    int rc = gb_check_launch("gb_residual_conv");
+    if (rc || !update_state || taps == 1) return rc;
+    dim3 grid2(S, gb_ceil_div(C, 256));
+    gb_launch(GB_PDL_ELEMENTWISE, residual_conv_state_kernel<T>, grid2, dim3(256), 0, stream, (const T*)x, state, state_stride, state_off,
+              seq_first_row, seq_start_pos, seq_slots, S, C, taps, num_slots);
+    return gb_check_launch("gb_residual_conv (state)");
+}
+
+GB_EXPORT int gb_residual_conv(const void* x, int dtype, const void* w, int w_dtype, void* y, float* state, long long state_stride,
+                               long long state_off, const int* row_seq, const int* positions, const int* seq_first_row,
+                               const int* seq_start_pos, const int* seq_slots, int n, int S, int C, int taps, int num_slots,
+                               int update_state, int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && S >= 0 && C > 0 && taps >= 1 && taps <= 64 && x != y, "gb_residual_conv: bad sizes (taps %d)", taps);
+    if (n == 0 || S == 0) return 0;
+#define RC_ARGS x, w, y, state, state_stride, state_off, row_seq, positions, seq_first_row, seq_start_pos, seq_slots, n, S, C, taps, \
+                num_slots, update_state, status, stream
+    if (dtype == GB_F32 && w_dtype == GB_F32) return residual_conv_launch<float, float>(RC_ARGS);
+    if (dtype == GB_BF16 && w_dtype == GB_BF16) return residual_conv_launch<__nv_bfloat16, __nv_bfloat16>(RC_ARGS);
+    if (dtype == GB_BF16 && w_dtype == GB_F32) return residual_conv_launch<__nv_bfloat16, float>(RC_ARGS);
+#undef RC_ARGS
+    GB_REQUIRE(false, "gb_residual_conv: unsupported dtypes %d / %d", dtype, w_dtype);
 }

@@ -37,6 +37,44 @@ GB_EXPORT int gb_embed(const void* table, int table_dtype, const int* tokens, fl
 }
 
 // ----------------------------------------------------------------------------------------------
+// Embedding with a learned vector per position: x[i, :] = table[tokens[i], :] + pos_table[positions[i], :], summed in float32.
+// Padding rows (position < 0) are cleared.
+// ----------------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_positions_kernel(const TW* __restrict__ table, const TW* __restrict__ pos_table, const int* __restrict__ tokens,
+                                       const int* __restrict__ positions, float* __restrict__ x, int n, int d, int vocab,
+                                       int max_position, int* __restrict__ status) {
+    int row = blockIdx.x;
+    if (row >= n) return;
+    const int tok = tokens[row], pos = positions[row];
+    const bool bad_tok = tok < 0 || tok >= vocab, bad_pos = pos >= max_position;
+    if (pos < 0 || bad_tok || bad_pos) {
+        if (threadIdx.x == 0 && pos >= 0) atomicOr(status, bad_tok ? GB_STATUS_BAD_TOKEN : GB_STATUS_BAD_POSITION);
+        for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)row * d + j] = 0.f;
+        return;
+    }
+    const TW* src = table + (size_t)tok * d;
+    const TW* ps = pos_table + (size_t)pos * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)row * d + j] = gb_to_float(src[j]) + gb_to_float(ps[j]);
+}
+
+GB_EXPORT int gb_embed_positions(const void* table, const void* pos_table, int table_dtype, const int* tokens, const int* positions,
+                                 float* x, int n, int d, int vocab, int max_position, int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && d > 0 && vocab > 0 && max_position > 0, "gb_embed_positions: bad sizes n=%d d=%d vocab=%d", n, d, vocab);
+    if (n == 0) return 0;
+    int threads = d >= 256 ? 256 : 128;
+    if (table_dtype == GB_F32)
+        embed_positions_kernel<float><<<n, threads, 0, stream>>>((const float*)table, (const float*)pos_table, tokens, positions, x, n, d,
+                                                                 vocab, max_position, status);
+    else if (table_dtype == GB_BF16)
+        embed_positions_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table,
+                                                                         tokens, positions, x, n, d, vocab, max_position, status);
+    else
+        GB_REQUIRE(false, "gb_embed_positions: unsupported table dtype %d", table_dtype);
+    return gb_check_launch("gb_embed_positions");
+}
+
+// ----------------------------------------------------------------------------------------------
 // RMSNorm: out_j = w_j * (x_j * rsqrt(mean(x^2) + eps))   (crates/glassbox-core/src/model.rs:94-100)
 // `rows` (optional) gathers input rows, used for the final norm on the wanted rows only.
 // ----------------------------------------------------------------------------------------------

@@ -7,7 +7,9 @@
 //   clamped_glu   act[r, f] = g * sigmoid(slope * g) * (u + 1), g = min(gate + b, limit), u = clamp(up + b, -limit, limit)
 //   relu2         out = max(in, 0)^2
 //   scale         t *= s
-//   gated_head_norm  out[r, h, :] = w * o[r, h, :] / sqrt(mean_v(o[r, h, :]^2) + eps) * sigmoid(gate[r, h, :])
+//   gated_head_norm  out[r, h, :] = w * o[r, h, :] / sqrt(mean_v(o[r, h, :]^2) + eps) * sigmoid(gate[r, h, :])  (or * silu(gate))
+//   gelu_glu      act[r, f] = gelu_tanh(gate[r, f]) * up[r, f]
+//   scaled_sum    out (+)= a * x + b * y
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------------------------
@@ -256,7 +258,7 @@ GB_EXPORT int gb_scale(float* t, long long total, float s, cudaStream_t stream) 
 template <typename T>
 __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate,
                                                               long long ldg, const float* __restrict__ w, T* __restrict__ out,
-                                                              int n, int heads, int v, float eps) {
+                                                              int n, int heads, int v, float eps, int gate_silu) {
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -272,22 +274,75 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     const float s = 1.0f / sqrtf(ss / (float)v + eps);
     for (int j = lane; j < v; j += 32) {
         const float sig = 1.0f / (1.0f + expf(-g[j]));
-        dst[j] = gb_from_float<T>(src[j] * s * w[j] * sig);
+        dst[j] = gb_from_float<T>(src[j] * s * w[j] * (gate_silu ? g[j] * sig : sig));
     }
 }
 
 GB_EXPORT int gb_gated_head_norm(const float* o, const float* gate, long long ldg, const float* w, void* out, int out_dtype,
-                                 int n, int heads, int v, float eps, cudaStream_t stream) {
+                                 int n, int heads, int v, float eps, int gate_silu, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && heads > 0 && v > 0, "gb_gated_head_norm: bad sizes");
     if (n == 0) return 0;
     const int blocks = gb_ceil_div((long long)n * heads, 4);
     if (out_dtype == GB_F32)
         gb_launch(GB_PDL_ELEMENTWISE, gated_head_norm_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, (float*)out, n,
-                  heads, v, eps);
+                  heads, v, eps, gate_silu);
     else if (out_dtype == GB_BF16)
         gb_launch(GB_PDL_ELEMENTWISE, gated_head_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w,
-                  (__nv_bfloat16*)out, n, heads, v, eps);
+                  (__nv_bfloat16*)out, n, heads, v, eps, gate_silu);
     else
         GB_REQUIRE(false, "gb_gated_head_norm: unsupported output dtype %d", out_dtype);
     return gb_check_launch("gb_gated_head_norm");
+}
+
+// ----------------------------------------------------------------------------------------------
+// The gated unit whose gate passes the tanh form of GELU: act[r, f] = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u with
+// g = gate_up[r, f], u = gate_up[r, ff + f]; float32 arithmetic, any input and output dtype.
+// ----------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) gelu_glu_kernel(const TI* __restrict__ gate_up, long long ld, TO* __restrict__ act, int n, int ff) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)n * ff) return;
+    const int r = (int)(i / ff), f = (int)(i % ff);
+    const float g = gb_to_float(gate_up[(size_t)r * ld + f]), u = gb_to_float(gate_up[(size_t)r * ld + ff + f]);
+    act[i] = gb_from_float<TO>(gb_gelu_tanh(g) * u);
+}
+
+GB_EXPORT int gb_gelu_glu(const void* gate_up, int in_dtype, long long ld, void* act, int out_dtype, int n, int ff, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && ff > 0 && ld >= 2 * ff, "gb_gelu_glu: bad sizes");
+    if (n == 0) return 0;
+    const int blocks = gb_ceil_div((long long)n * ff, 256);
+    if (in_dtype == GB_F32 && out_dtype == GB_F32)
+        gb_launch(GB_PDL_ELEMENTWISE, gelu_glu_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, ld, (float*)act, n, ff);
+    else if (in_dtype == GB_F32 && out_dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, gelu_glu_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, ld,
+                  (__nv_bfloat16*)act, n, ff);
+    else if (in_dtype == GB_BF16 && out_dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, gelu_glu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                  (const __nv_bfloat16*)gate_up, ld, (__nv_bfloat16*)act, n, ff);
+    else
+        GB_REQUIRE(false, "gb_gelu_glu: unsupported dtypes %d -> %d", in_dtype, out_dtype);
+    return gb_check_launch("gb_gelu_glu");
+}
+
+// ----------------------------------------------------------------------------------------------
+// out[r, :] (+)= a * x[r, :] + b * y[r, :]: two branches that share an input join with a weight each. Float32.
+// ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) scaled_sum_kernel(const float* __restrict__ x, const float* __restrict__ y, float a, float b,
+                                                         float* __restrict__ out, long long count, int accumulate) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= count) return;
+    const float v = fmaf(a, x[i], b * y[i]);
+    out[i] = accumulate ? out[i] + v : v;
+}
+
+GB_EXPORT int gb_scaled_sum(const float* x, const float* y, float a, float b, float* out, long long count, int accumulate,
+                            cudaStream_t stream) {
+    GB_REQUIRE(count >= 0, "gb_scaled_sum: bad size");
+    if (count == 0) return 0;
+    gb_launch(GB_PDL_ELEMENTWISE, scaled_sum_kernel, dim3(gb_ceil_div(count, 256)), dim3(256), 0, stream, x, y, a, b, out, count, accumulate);
+    return gb_check_launch("gb_scaled_sum");
 }

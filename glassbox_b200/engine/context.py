@@ -12,7 +12,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..cache.device import DeviceCache, PagedLayerView
+from ..cache.device import CombinedLayerView, DeviceCache, PagedLayerView
 
 
 @dataclass
@@ -152,7 +152,8 @@ class StepContext:
 
     def cache_view(self, cache_layer: int):
         view = self.cache.layer_view(cache_layer)
-        if isinstance(view, PagedLayerView):
-            view.slots = self.group_slots[view.group]
-            view.block_tables = self.group_tables[view.group]
+        paged = view.paged if isinstance(view, CombinedLayerView) else view
+        if isinstance(paged, PagedLayerView):
+            paged.slots = self.group_slots[paged.group]
+            paged.block_tables = self.group_tables[paged.group]
         return view

@@ -76,15 +76,20 @@ class DecoderModel:
     def cache_layer_specs(self) -> List[object]:
         """The cache spec of each cache layer: that of the mixer of the run that writes it."""
         specs: List[object] = [None] * self.config.num_cache_layers
+
+        def needs(layer):
+            # a layer that keeps something of its own beside its mixer's cache says so itself
+            if hasattr(layer, "cache_spec"):
+                return layer.cache_spec()
+            mixer = getattr(layer, "mixer", None)
+            return mixer.cache_spec() if mixer is not None else None
+
         for run in self.config.schedule:
-            mixer = getattr(self.layers[run.layer], "mixer", None)
-            spec = mixer.cache_spec() if mixer is not None else None
             if run.writes_cache:
-                specs[run.cache] = spec
+                specs[run.cache] = needs(self.layers[run.layer])
         for run in self.config.schedule:
             if not run.writes_cache:
-                mixer = getattr(self.layers[run.layer], "mixer", None)
-                spec = mixer.cache_spec() if mixer is not None else None
+                spec = needs(self.layers[run.layer])
                 if spec != specs[run.cache]:
                     raise ValueError(f"a run of layer {run.layer} reads cache layer {run.cache}, whose writer keeps "
                                      f"{specs[run.cache]!r}, but needs {spec!r}")

@@ -18,6 +18,9 @@ from .csrc import build as _build
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
+#: the gate functions that the products' gated epilogues know (act = f(gate) * up)
+GATED_EPILOGUES = ("silu",)
+
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot or page id outside the pool",
                4: "a position outside the rotary table or beyond a block table", 8: "a bounded wait inside a kernel gave up"}
 
@@ -87,7 +90,7 @@ _SIGNATURES = {
     "gb_clamped_glu": [_P, _I, _LL, _P, _F, _F, _P, _I, _I, _I, _P],
     "gb_relu2": [_P, _P, _I, _LL, _P],
     "gb_scale": [_P, _LL, _F, _P],
-    "gb_gated_head_norm": [_P, _P, _LL, _P, _P, _I, _I, _I, _I, _F, _P],
+    "gb_gated_head_norm": [_P, _P, _LL, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "gb_latent_kv_write": [_P, _LL, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_latent_attention_rows": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_latent_attention_mma_supported": [_I, _I, _I],
@@ -95,11 +98,18 @@ _SIGNATURES = {
                                 _P, _P],
     "gb_head_linear_supported": [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I],
     "gb_head_linear": [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _P],
+    "gb_embed_positions": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "gb_residual_conv": [_P, _I, _P, _I, _P, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gb_gelu_glu": [_P, _I, _LL, _P, _I, _I, _I, _P],
+    "gb_scaled_sum": [_P, _P, _F, _F, _P, _LL, _I, _P],
+    "gb_bias_rope_write": [_P, _LL, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _LL, _I, _P, _P],
+    "gb_talking_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
+    "gb_talk_combine": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
-    "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P],
     "gb_channel_delta_decode_supported": [_I, _I],
     "gb_channel_delta_decode": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _LL, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                                _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _P],
+                                _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "gb_streams_broadcast": [_P, _P, _I, _I, _I, _P],
     "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _I, _P, _LL, _P, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
@@ -355,6 +365,17 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: to
     n, d = x.shape
     assert tokens.dtype == torch.int32 and x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous()
     _call("gb_embed", _ptr(table), _dt(table), _ptr(tokens), _ptr(x), n, d, table.shape[0], float(scale), _ptr(status), _stream())
+
+
+def embed_positions(table: torch.Tensor, pos_table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, x: torch.Tensor,
+                    status: torch.Tensor) -> None:
+    """x[i, :] = table[tokens[i], :] + pos_table[positions[i], :], summed in float32; padding rows (position < 0) are cleared."""
+    _cuda(table, pos_table, tokens, positions, x, status)
+    n, d = x.shape
+    assert table.dtype == pos_table.dtype and table.shape[1] == pos_table.shape[1] == d and x.dtype == torch.float32
+    assert table.is_contiguous() and pos_table.is_contiguous() and x.is_contiguous() and tokens.shape[0] >= n and positions.shape[0] >= n
+    _call("gb_embed_positions", _ptr(table), _ptr(pos_table), _dt(table), _ptr(tokens), _ptr(positions), _ptr(x), n, d, table.shape[0],
+          pos_table.shape[0], _ptr(status), _stream())
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float,
@@ -976,7 +997,8 @@ def scale_(t: torch.Tensor, s: float) -> None:
     _call("gb_scale", _ptr(t), t.numel(), float(s), _stream())
 
 
-def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, eps: float) -> None:
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, eps: float,
+                    gate_silu: bool = False) -> None:
     """out[r, h, :] = weight * o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * sigmoid(gate[r, h, :]); o, gate, weight
     float32 (gate may be a column slice of a wider tensor)."""
     _cuda(o, gate, weight, out)
@@ -985,7 +1007,23 @@ def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, o
     assert o.dtype == gate.dtype == weight.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
     assert gate.shape == (n, hv) and gate.stride(1) == 1 and out.shape == (n, hv) and weight.numel() == v
     _call("gb_gated_head_norm", _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), _dt(out), n, heads, v, float(eps),
-          _stream())
+          1 if gate_silu else 0, _stream())
+
+
+def gelu_glu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act[r, f] = gelu_tanh(gate_up[r, f]) * gate_up[r, ff + f], the tanh form of GELU on the gate half; float32 arithmetic."""
+    _cuda(gate_up, act)
+    n, ff = act.shape
+    assert gate_up.shape == (n, 2 * ff) and gate_up.stride(1) == 1 and act.is_contiguous()
+    _call("gb_gelu_glu", _ptr(gate_up), _dt(gate_up), gate_up.stride(0), _ptr(act), _dt(act), n, ff, _stream())
+
+
+def scaled_sum(x: torch.Tensor, y: torch.Tensor, a: float, b: float, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (+)= a * x + b * y; float32, same shapes, contiguous."""
+    _cuda(x, y, out)
+    assert x.dtype == y.dtype == out.dtype == torch.float32 and x.shape == y.shape == out.shape
+    assert x.is_contiguous() and y.is_contiguous() and out.is_contiguous()
+    _call("gb_scaled_sum", _ptr(x), _ptr(y), float(a), float(b), _ptr(out), x.numel(), 1 if accumulate else 0, _stream())
 
 
 # ------------------------------------------------------------------------------- attention over a latent cache
@@ -1102,22 +1140,62 @@ def short_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torch.T
 def channel_delta(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
                   state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
                   seq_slots: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, write_state: bool,
-                  status: torch.Tensor) -> None:
-    """The gated delta rule with a decay per head and key channel, token by token along each request's rows, from and to
-    the request's slot of ``state`` [slots, numbers] (S = [heads, dk, dv] first). qkv float32 [n, 2 * kv_heads * dk + heads * dv]
-    (q, k, v after their convolutions), beta [n, heads] and a [n, heads * dk] logits (column slices allowed);
-    out float32 [n, heads * dv] is the read-out before its norm."""
+                  status: torch.Tensor, decay_per_head: bool = False) -> None:
+    """The gated delta rule, token by token along each request's rows, from and to the request's slot of ``state`` [slots,
+    numbers] (S = [heads, dk, dv] first). qkv float32 [n, 2 * kv_heads * dk + heads * dv] (q, k, v after their
+    convolutions), beta [n, heads] logits, a the decay's logits: [n, heads * dk] with ``dt_bias`` [heads * dk] (a decay per
+    head and key channel) or, with ``decay_per_head``, [n, heads] and [heads] (column slices allowed); out float32
+    [n, heads * dv] is the read-out before its norm."""
     _cuda(qkv, beta, a, dt_bias, a_log, state, out, seq_first_row, seq_start_pos, seq_slots, status)
     n = qkv.shape[0]
+    dc = 1 if decay_per_head else dk
     for t in (qkv, beta, a, dt_bias, a_log, state, out):
         assert t.dtype == torch.float32
     assert qkv.shape[1] == 2 * kv_heads * dk + heads * dv and qkv.stride(1) == 1 and beta.shape == (n, heads)
-    assert a.shape == (n, heads * dk) and a.stride(1) == 1 and beta.stride(1) == 1 and out.shape == (n, heads * dv)
+    assert a.shape == (n, heads * dc) and a.stride(1) == 1 and beta.stride(1) == 1 and out.shape == (n, heads * dv)
     assert out.is_contiguous() and state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv
-    assert dt_bias.numel() == heads * dk and a_log.numel() == heads
+    assert dt_bias.numel() == heads * dc and a_log.numel() == heads
     _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(a), a.stride(0), _ptr(dt_bias),
           _ptr(a_log), _ptr(state), state.stride(0), _ptr(out), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots),
-          seq_start_pos.shape[0], heads, kv_heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status), _stream())
+          seq_start_pos.shape[0], heads, kv_heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status), dc, 0, _stream())
+
+
+CD_SILU_INPUTS, CD_PLAIN, CD_GATE_SILU = 1, 2, 4
+
+
+def decay_linear_attention(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,
+                           seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int, dk: int, dv: int, write_state: bool,
+                           status: torch.Tensor, silu_inputs: bool = True) -> None:
+    """Linear attention with a fixed decay per head, token by token along each request's rows, on the delta rule's kernel
+    with the correction switched off: S <- decay_h S + k v^T, o = S^T q, S float32 [heads, dk, dv] at the start of the
+    request's slot of ``state``. qkv float32 [n, 2 * heads * dk + heads * dv] (column slice allowed); with ``silu_inputs``
+    q, k and v pass SiLU as they are read. decay float32 [heads]; out float32 [n, heads * dv]."""
+    _cuda(qkv, decay, state, out, seq_first_row, seq_start_pos, seq_slots, status)
+    n = qkv.shape[0]
+    for t in (qkv, decay, state, out):
+        assert t.dtype == torch.float32
+    assert qkv.shape[1] == 2 * heads * dk + heads * dv and qkv.stride(1) == 1 and out.shape == (n, heads * dv) and out.is_contiguous()
+    assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and decay.numel() == heads
+    _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), 0, 0, 0, 0, 0, _ptr(decay), _ptr(state), state.stride(0), _ptr(out),
+          _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, heads, dk, dv, state.shape[0],
+          1 if write_state else 0, _ptr(status), 1, CD_PLAIN | (CD_SILU_INPUTS if silu_inputs else 0), _stream())
+
+
+def residual_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torch.Tensor, state_off: int, row_seq: torch.Tensor,
+                  positions: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor,
+                  update_state: bool, status: torch.Tensor) -> None:
+    """y[t, c] = x[t, c] + sum_j w[c, j] * x[t - (taps - 1) + j, c] along each request's rows (x, y [n, C] in the activation
+    dtype, different buffers; sums in float32). Inputs from before the step come from (and, with ``update_state``, the last
+    taps - 1 inputs go to) the request's slot of ``state`` float32 [slots, numbers], at ``state_off``, laid out [taps - 1, C]."""
+    _cuda(x, w, y, state, row_seq, positions, seq_first_row, seq_start_pos, seq_slots, status)
+    n, C = x.shape
+    taps = w.shape[1]
+    assert y.shape == (n, C) and x.is_contiguous() and y.is_contiguous() and x.dtype == y.dtype and w.shape == (C, taps) and w.is_contiguous()
+    assert x.data_ptr() != y.data_ptr() and state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    assert state_off + (taps - 1) * C <= state.shape[1]
+    _call("gb_residual_conv", _ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(y), _ptr(state), state.stride(0), state_off, _ptr(row_seq),
+          _ptr(positions), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), n, seq_start_pos.shape[0], C, taps, state.shape[0],
+          1 if update_state else 0, _ptr(status), _stream())
 
 
 def channel_delta_decode_supported(dk: int, dv: int) -> bool:
@@ -1144,7 +1222,8 @@ def channel_delta_decode(qkv: Optional[torch.Tensor], beta: torch.Tensor, a: Opt
                          a_log: torch.Tensor, state: torch.Tensor, gate: Optional[torch.Tensor], norm_weight: torch.Tensor,
                          eps: float, att: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
                          seq_slots: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, write_state: bool,
-                         status: torch.Tensor, fusion: Optional[DeltaDecodeFusion] = None) -> None:
+                         status: torch.Tensor, fusion: Optional[DeltaDecodeFusion] = None, decay_per_head: bool = False,
+                         gate_silu: bool = False) -> None:
     """``channel_delta`` for a step in which every request brings one row, with the read-out's norm and gate applied as
     well: ``att`` [n, heads * dv] (any activation dtype) = norm_weight * o / rms(o) * sigmoid(gate). Reads and writes
     each request's S once, in whole rows. With ``fusion`` the kernel also computes the convolutions of q, k, v (reading
@@ -1159,7 +1238,8 @@ def channel_delta_decode(qkv: Optional[torch.Tensor], beta: torch.Tensor, a: Opt
     if fusion is None:
         for t in (qkv, a, gate):
             assert t.dtype == torch.float32 and t.stride(1) == 1
-        assert qkv.shape == (n, 2 * kv_heads * dk + heads * dv) and a.shape == (n, heads * dk) and gate.shape == (n, heads * dv)
+        assert qkv.shape == (n, 2 * kv_heads * dk + heads * dv) and gate.shape == (n, heads * dv)
+        assert a.shape == (n, heads * (1 if decay_per_head else dk)) and dt_bias.numel() == a.shape[1]
         extra = (0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0)
         ptrs = (_ptr(qkv), qkv.stride(0), _ptr(a), a.stride(0), _ptr(gate), gate.stride(0))
     else:
@@ -1179,7 +1259,8 @@ def channel_delta_decode(qkv: Optional[torch.Tensor], beta: torch.Tensor, a: Opt
     _call("gb_channel_delta_decode", ptrs[0], ptrs[1], _ptr(beta), beta.stride(0), ptrs[2], ptrs[3], _ptr(dt_bias),
           _ptr(a_log), _ptr(state), state.stride(0), ptrs[4], ptrs[5], _ptr(norm_weight), float(eps), _ptr(att),
           _dt(att), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, kv_heads, dk, dv,
-          state.shape[0], 1 if write_state else 0, _ptr(status), *extra, _stream())
+          state.shape[0], 1 if write_state else 0, _ptr(status), *extra, 1 if decay_per_head else dk,
+          CD_GATE_SILU if gate_silu else 0, _stream())
 
 
 def short_conv_state(x: torch.Tensor, state: torch.Tensor, state_off: int, taps: int, seq_first_row: torch.Tensor,
@@ -1529,3 +1610,54 @@ def moe_combine(pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch
     assert shared is None or (shared.dtype == torch.float32 and shared.shape == (n, d) and shared.stride(1) == 1)
     _call("gb_moe_combine", _ptr(pair), _ptr(weight), top, _ptr(shared), shared.stride(0) if shared is not None else 0, _ptr(gate),
           _ptr(positions), _ptr(out), out.stride(0), n, d, 1 if accumulate else 0, _stream())
+
+
+# ------------------------------------------------------------------------------ attention whose heads exchange their weights
+def bias_rope_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
+                    slots: torch.Tensor, q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, heads: int, kv_heads: int,
+                    dim: int, vdim: int, rot: int, page_size: int, write_kv: bool, status: torch.Tensor) -> None:
+    """From the float32 sums of the stacked projection q | k | v: ``bias`` (float32, one number per column, or None) is added,
+    the first ``rot`` channels of every query and key head are rotated (channel i with channel i + rot/2, by the (cos, sin) of
+    ``cos_sin`` [positions, rot/2, 2] at the row's position), q goes to ``q_out`` [n, heads * dim], k and v into the paged
+    cache at each row's slot."""
+    _cuda(qkv, bias, cos_sin, positions, slots, q_out, kcache, vcache, status)
+    n = qkv.shape[0]
+    cols = (heads + kv_heads) * dim + kv_heads * vdim
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == cols
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == cols and bias.is_contiguous())
+    assert q_out.shape == (n, heads * dim) and q_out.is_contiguous() and q_out.dtype == kcache.dtype == vcache.dtype
+    assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[-1] == dim and vcache.shape[-1] == vdim
+    assert rot == 0 or (cos_sin is not None and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+                        and tuple(cos_sin.shape[1:]) == (rot // 2, 2))
+    _call("gb_bias_rope_write", _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(cos_sin), cos_sin.shape[0] if cos_sin is not None else 0,
+          _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(kcache), _ptr(vcache), _dt(q_out), n, heads, kv_heads, dim, vdim, rot, page_size,
+          kcache.shape[0] * page_size, 1 if write_kv else 0, _ptr(status), _stream())
+
+
+def talking_attention_rows(q: torch.Tensor, wide: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                           row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                           value_heads: int, page_size: int, scale: float, softcap: Optional[float], unit_sink: bool,
+                           window: Optional[int], status: torch.Tensor) -> None:
+    """wide[row, g, c, :] = sum over the row's visible keys j of w_g(j) * v_c(j), float32 [n, heads * value_heads * vdim], with
+    w_g the softmax of head g's (capped) scores whose denominator holds one more unit when ``unit_sink``; ``value_heads`` is
+    ``kv_heads`` (every key/value head's values, what a mix of the heads needs) or 1 (the head's own). One warp per (row, head)."""
+    _cuda(q, wide, kcache, vcache, block_tables, row_seq, positions, status)
+    n = q.shape[0]
+    assert q.shape == (n, heads * dim) and q.is_contiguous() and q.dtype == kcache.dtype == vcache.dtype
+    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert block_tables.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous()
+    _call("gb_talking_attention_rows", _ptr(q), _ptr(wide), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(row_seq), _ptr(positions), n, heads, kv_heads, dim, vdim, value_heads, page_size, kcache.shape[0], float(scale),
+          float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), _ptr(status), _stream())
+
+
+def talk_combine(wide: torch.Tensor, talk: Optional[torch.Tensor], att: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int,
+                 vdim: int, value_heads: int) -> None:
+    """att[row, h, :] = sum_g talk[h, g] * wide[row, g, c(h), :] with c(h) the key/value head of h (``talk`` None: head h's own
+    result as it is); talk float32 [heads, heads]."""
+    _cuda(wide, talk, att, positions)
+    n = att.shape[0]
+    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert att.shape == (n, heads * vdim) and att.is_contiguous()
+    assert talk is None or (talk.dtype == torch.float32 and talk.shape == (heads, heads) and talk.is_contiguous())
+    _call("gb_talk_combine", _ptr(wide), _ptr(talk), _ptr(att), _dt(att), _ptr(positions), n, heads, kv_heads, vdim, value_heads, _stream())

@@ -1,2 +1,2 @@
 """Architectures. Importing this package registers them."""
-from . import llama, lonorax, tagenex, zurerax  # noqa: F401
+from . import babotar, llama, lonorax, tagenex, zurerax  # noqa: F401

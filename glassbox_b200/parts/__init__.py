@@ -1,8 +1,8 @@
 """The parts a layer is put together from. Importing this package registers the built-in parts."""
 from .base import (FeedForward, Mixer, Norm, OutputHead, PagedKvSpec, Part, Position, StateSpec, TokenEmbedding, build_part,
                    register_part, registered)
-from . import (attention, block, delta_rule, embedding, latent_attention, mingru, mlp, moe, norm, rope, sigmoid_attention,
-               sink_attention)  # noqa: F401  (registration)
+from . import (attention, block, delta_rule, embedding, latent_attention, linear_attention, mingru, mlp, moe, norm, parallel, rope,
+               sigmoid_attention, sink_attention, talking_attention)  # noqa: F401  (registration)
 from .block import build_block
 from .embedding import Embedding, LmHead
 

@@ -56,6 +56,49 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class CombinedCacheSpec:
+    """What a cache layer keeps when one kind is not enough: keys and values in pages (``paged``, or None) and any number of
+    named fixed-size states per request (``states``: pairs of a name and a ``StateSpec``). A mixer made of two mixers, or
+    a layer that keeps something of its own beside its mixer's cache, declares this; the cache view then carries the pages
+    and a tensor per name (``CombinedLayerView``)."""
+    paged: Optional[PagedKvSpec] = None
+    states: Tuple[Tuple[str, StateSpec], ...] = ()
+
+
+def combine_cache_specs(named) -> object:
+    """One cache spec for several users of one cache layer. ``named``: pairs (name, spec); a ``StateSpec`` becomes the
+    state called name, a ``CombinedCacheSpec``'s states are prefixed with "name.", at most one user may keep pages. With
+    a single user that needs no renaming the spec is returned as it is."""
+    named = [(n, s) for n, s in named if s is not None]
+    if len(named) == 1 and named[0][0] == "":
+        return named[0][1]
+    paged, states = None, []
+    for name, spec in named:
+        prefix = name + "." if name else ""
+        if isinstance(spec, StateSpec):
+            states.append((name or "state", spec))
+            continue
+        if isinstance(spec, CombinedCacheSpec):
+            states.extend((prefix + n, s) for n, s in spec.states)
+            spec = spec.paged
+        if spec is not None:
+            if paged is not None:
+                raise ValueError("only one user of a cache layer may keep keys and values in pages")
+            paged = spec
+    if not states:
+        return paged
+    return CombinedCacheSpec(paged, tuple(states))
+
+
+def sub_view(view, name: str, spec):
+    """The cache view of the user called ``name`` (which declared ``spec``) of a cache layer whose whole view is ``view``: a
+    combined view hands out the part, a plain one belongs to its single user."""
+    if spec is None:
+        return None
+    return view.part(name, spec) if hasattr(view, "part") else view
+
+
 class Part:
     #: True when every piece of device work this part does is a call into ``glassbox_b200.kernels``. Only then may
     #: its calls be recorded into a decode program and run later, in order, by one persistent kernel; a part that

@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels
 from ..weights.binding import ParamSpec
-from .base import DeferredNorm, Part, build_part, register_part
+from .base import DeferredNorm, Part, StateSpec, build_part, combine_cache_specs, register_part, sub_view
 from .norm import ResidualItself
 
 
@@ -196,14 +196,56 @@ class StreamMixing(Part):
     ``mix`` [S, S], indexed [from, to] (how the streams feed one another meanwhile). Float32."""
     launches_through_kernels_only = True
 
-    def __init__(self, streams: int):
+    def __init__(self, streams: int, learned: bool = True, scale: float = 1.0):
+        """``learned`` False: no tensors; the branch reads the plain sum, every stream keeps itself and takes the output
+        once. ``scale`` multiplies the branch's output on its way into the streams (it is folded into ``write`` once, in
+        float32, when the weights arrive)."""
         super().__init__(None)
-        self.streams = streams
+        self.streams, self.learned, self.scale = streams, learned, float(scale)
 
     def param_specs(self):
+        if not self.learned:
+            return {}
         s = self.streams
         return {"read": ParamSpec((s,), role="gain", init=(1.0 / s, 0.1 / s)), "write": ParamSpec((s,), role="gain", init=(1.0, 0.1)),
                 "mix": ParamSpec((s, s), role="gain", init=(1.0 / s, 0.1 / s))}
+
+    def bind(self, params) -> None:
+        super().bind(params)
+        if self.learned and self.scale != 1.0:
+            self.params["write"] = (self.params["write"].float() * self.scale).contiguous()
+
+    def on_device(self, device):
+        """(read, mix, write) as the kernel takes them; the constants of an unlearned mixing are made at first use."""
+        if not self.learned and "write" not in self.params:
+            s = self.streams
+            self.params = {"read": torch.ones(s, dtype=torch.float32, device=device),
+                           "mix": torch.eye(s, dtype=torch.float32, device=device).contiguous(),
+                           "write": torch.full((s,), self.scale, dtype=torch.float32, device=device)}
+        return self.params["read"], self.params["mix"], self.params["write"]
+
+
+class InputConvolution(Part):
+    """A causal convolution over time, per channel, added to its own input: h_t <- h_t + sum_j w[:, j] h_(t - taps + 1 + j),
+    zeros before a sequence's start; ``weight`` [channels, taps], the last column weighs the current token. The last
+    taps - 1 inputs are kept per request (float32) so that a sequence may arrive in portions."""
+    launches_through_kernels_only = True
+
+    def __init__(self, channels: int, taps: int):
+        super().__init__(None)
+        if not 1 <= taps <= 64:
+            raise ValueError(f"a convolution of {taps} taps is outside 1..64")
+        self.channels, self.taps = channels, taps
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.channels, self.taps), role="gain", init=(0.0, 0.3))}
+
+    def cache_spec(self):
+        return StateSpec((max(self.taps - 1, 1) * self.channels,), torch.float32)
+
+    def forward(self, ctx, h, out, state, writes_cache: bool) -> None:
+        kernels.residual_conv(h, self.params["weight"], out, state, 0, ctx.row_seq, ctx.positions, ctx.seq_first_row,
+                              ctx.seq_start_pos, ctx.seq_slots, writes_cache, ctx.status)
 
 
 class HyperConnectionBlock(Part):
@@ -222,30 +264,45 @@ class HyperConnectionBlock(Part):
         self.hidden_size, self.streams = hidden_size, spec.streams
         self.mixer_norm = build_part("norm", spec.mixer_norm, hidden_size=hidden_size)
         self.mixer = build_part("mixer", spec.mixer, hidden_size=hidden_size)
-        self.mixer_streams = StreamMixing(spec.streams)
+        learned, scale = getattr(spec, "learned_streams", True), getattr(spec, "branch_scale", 1.0)
+        self.mixer_streams = StreamMixing(spec.streams, learned, scale)
+        taps = getattr(spec, "mixer_input_conv", 0)
+        self.mixer_conv = InputConvolution(hidden_size, taps) if taps else None
         self.ffn = self.ffn_norm = self.ffn_streams = None
         if spec.ffn is not None:
             self.ffn_norm = build_part("norm", spec.ffn_norm, hidden_size=hidden_size)
             self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
-            self.ffn_streams = StreamMixing(spec.streams)
+            self.ffn_streams = StreamMixing(spec.streams, learned, scale)
 
     def sub_parts(self):
         parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_streams": self.mixer_streams}
+        if self.mixer_conv is not None:
+            parts["mixer_conv"] = self.mixer_conv
         if self.ffn is not None:
             parts.update({"ffn_norm": self.ffn_norm, "ffn": self.ffn, "ffn_streams": self.ffn_streams})
         return parts
 
-    def _branch(self, ctx, part, norm, mixing, xs, run) -> None:
+    def cache_spec(self):
+        """What this layer's cache layer keeps: the mixer's cache and, with a convolution on the mixer's input, its last
+        inputs."""
+        if self.mixer_conv is None:
+            return self.mixer.cache_spec()
+        return combine_cache_specs([("mixer", self.mixer.cache_spec()), ("input_conv", self.mixer_conv.cache_spec())])
+
+    def _branch(self, ctx, part, norm, mixing, xs, run, conv=None) -> None:
         n, d = xs.shape[0], self.hidden_size
         h = ctx.scratch("h", (n, d))
         fold, ctx.pending_fold = getattr(ctx, "pending_fold", None), None
+        read, mix, write = mixing.on_device(xs.device)
         as_ln = getattr(norm, "as_layernorm", None)
         if as_ln is not None:
-            kernels.streams_step(xs, self.streams, fold=fold, read=mixing.params["read"], norm=as_ln(), h=h, positions=ctx.positions)
+            kernels.streams_step(xs, self.streams, fold=fold, read=read, norm=as_ln(), h=h, positions=ctx.positions)
         else:
             u = ctx.scratch("stream_mix", (n, d), torch.float32)
-            kernels.streams_step(xs, self.streams, fold=fold, read=mixing.params["read"], u_out=u, positions=ctx.positions)
+            kernels.streams_step(xs, self.streams, fold=fold, read=read, u_out=u, positions=ctx.positions)
             norm.forward(ctx, u, h)
+        if conv is not None:
+            h = conv(h)
         y = ctx.scratch("branch", (n, d), torch.float32)
         ctx.overwrite_output = bool(part.can_overwrite_output)
         if not ctx.overwrite_output:
@@ -258,12 +315,21 @@ class HyperConnectionBlock(Part):
         finally:
             ctx.overwrite_output = ctx.accepts_weighted_rows = False
         out, ctx.weighted_rows = (ctx.weighted_rows if ctx.weighted_rows is not None else y), None
-        ctx.pending_fold = (out, mixing.params["mix"], mixing.params["write"])
+        ctx.pending_fold = (out, mix, write)
 
     def forward(self, ctx, xs, cache, writes_cache: bool, after_mixer=None) -> None:
         ctx.next_norm = ctx.prepared_norm = None      # no product of this layer completes residual rows
+        conv = None
+        if self.mixer_conv is not None:
+            conv_state = cache.states["input_conv"]
+            cache = sub_view(cache, "mixer", self.mixer.cache_spec())
+
+            def conv(h):
+                out = ctx.scratch("h_conv", tuple(h.shape))
+                self.mixer_conv.forward(ctx, h, out, conv_state, writes_cache)
+                return out
         self._branch(ctx, self.mixer, self.mixer_norm, self.mixer_streams, xs,
-                     lambda h, out: self.mixer.forward(ctx, h, out, cache, writes_cache))
+                     lambda h, out: self.mixer.forward(ctx, h, out, cache, writes_cache), conv=conv)
         if after_mixer is not None:
             after_mixer()
         if self.ffn is not None:

@@ -40,6 +40,17 @@ class LmHead(OutputHead):
         linear(ctx, hs, self.params["weight"], logits)
 
 
+class PositionalEmbedding(Embedding):
+    """x[i, :] = E[token_i, :] + P[position_i, :]: a learned vector per position, neither table scaled, the sum in float32."""
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.vocab_size, self.hidden_size)),
+                "positions": ParamSpec((self.spec.max_position, self.hidden_size))}
+
+    def forward(self, ctx, tokens, x) -> None:
+        kernels.embed_positions(self.params["weight"], self.params["positions"], tokens, ctx.positions, x, ctx.status)
+
+
 class ScaledEmbedding(Embedding):
     """x[i, :] = E[token_i, :] * scale, the product in float32."""
 
@@ -58,5 +69,6 @@ class ScaledLmHead(LmHead):
 
 register_part("embedding", "embedding", Embedding, replace=True)
 register_part("embedding", "scaled_embedding", ScaledEmbedding, replace=True)
+register_part("embedding", "positional_embedding", PositionalEmbedding, replace=True)
 register_part("head", "scaled_lm_head", ScaledLmHead, replace=True)
 register_part("head", "lm_head", LmHead, replace=True)

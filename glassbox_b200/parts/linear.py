@@ -91,9 +91,12 @@ def linear(ctx, a, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False)
         kernels.gemm_simt(x, w, out, accumulate)
 
 
-def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
+def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor, unit: str = "silu") -> bool:
     """act = silu(a Wgate^T) * (a Wup^T) in one kernel when the shape allows; returns False (and
-    does nothing) otherwise, and the caller runs the product and the activation separately."""
+    does nothing) otherwise, and the caller runs the product and the activation separately. ``unit`` names the gate's
+    function; a unit for which the products have no epilogue is never fused."""
+    if unit not in kernels.GATED_EPILOGUES:
+        return False
     inter = w_gate_up.shape[0] // 2
     x, norm, _, scale = _resolve(a, w_gate_up)
     if scale is not None:

@@ -34,6 +34,33 @@ class SwiGlu(FeedForward):
         linear(ctx, act, self.params["w_down"], residual, accumulate=True)
 
 
+class GeluGlu(FeedForward):
+    """Dense gated feed-forward whose gate passes the tanh form of GELU: residual += (gelu_tanh(h Wgate^T) * (h Wup^T)) Wdown^T,
+    gate rows then up rows stacked in one matrix, no bias. The unit is formed in float32 from the float32 sums of the first
+    product."""
+    accepts_deferred_input = True
+    launches_through_kernels_only = True
+    can_overwrite_output = True
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        self.hidden_size = hidden_size
+        self.inter = spec.intermediate_size
+
+    def param_specs(self):
+        d, i = self.hidden_size, self.inter
+        return {"w_gate_up": ParamSpec((2 * i, d), pieces=(i, i)), "w_down": ParamSpec((d, i))}
+
+    def forward(self, ctx, h, residual) -> None:
+        n = h.shape[0]
+        act = ctx.scratch("act", (n, self.inter))
+        if not gated_linear(ctx, h, self.params["w_gate_up"], act, unit="gelu_tanh"):
+            gate_up = ctx.scratch("gate_up32", (n, 2 * self.inter), torch.float32)
+            linear(ctx, h, self.params["w_gate_up"], gate_up)
+            kernels.gelu_glu(gate_up, act)
+        linear(ctx, act, self.params["w_down"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
+
+
 class SquaredRelu(FeedForward):
     """Dense feed-forward without a gate: residual += (relu(h Wup^T))^2 Wdown^T, no bias."""
     accepts_deferred_input = True
@@ -101,4 +128,5 @@ class ClampedGlu(FeedForward):
 
 register_part("ffn", "clamped_glu", ClampedGlu, replace=True)
 register_part("ffn", "swiglu", SwiGlu, replace=True)
+register_part("ffn", "gelu_glu", GeluGlu, replace=True)
 register_part("ffn", "relu2", SquaredRelu, replace=True)

@@ -8,21 +8,43 @@ long positions round "like transformers" (model.rs:106), so it is kept.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
 from .base import Position, register_part
 
 
-def rotary_table(theta: float, rotary_dim: int, max_position: int) -> torch.Tensor:
-    """float32 [max_position, rotary_dim/2, 2] holding (cos, sin)."""
+def rescaled_frequencies(theta: float, rotary_dim: int, rescale):
+    """(float64 frequencies [rotary_dim/2], the factor on sine and cosine) of a rotation whose frequencies are stretched by
+    wavelength (``RopeRescaleSpec``): pair i turns f_i = theta^(-2i / rotary_dim) radians per token; with dim(t) = rotary_dim *
+    ln(original / (2 pi t)) / (2 ln theta) the pair index that makes t turns within the original context, the pairs below
+    lo = max(floor(dim(fast)), 0) keep f_i, those above hi = min(ceil(dim(slow)), rotary_dim - 1) get f_i / factor, the
+    ones between a blend along the ramp clamp((i - lo) / max(hi - lo, 0.001), 0, 1)."""
     half = rotary_dim // 2
     i = np.arange(half, dtype=np.float64)
-    inv = (1.0 / np.power(np.float64(theta), 2.0 * i / np.float64(rotary_dim))).astype(np.float32)
+    f = np.power(np.float64(theta), -2.0 * i / np.float64(rotary_dim))
+    if rescale is None:
+        return f, 1.0
+
+    def pair_of(turns: float) -> float:
+        return rotary_dim * math.log(rescale.original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_of(rescale.fast)), 0)
+    hi = min(math.ceil(pair_of(rescale.slow)), rotary_dim - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / rescale.factor * ramp + f * (1.0 - ramp), rescale.magnitude_slope * math.log(rescale.factor) + 1.0
+
+
+def rotary_table(theta: float, rotary_dim: int, max_position: int, rescale=None) -> torch.Tensor:
+    """float32 [max_position, rotary_dim/2, 2] holding (cos, sin), times the rescaling's factor if there is one."""
+    freq, magnitude = rescaled_frequencies(theta, rotary_dim, rescale)
+    inv = freq.astype(np.float32)
     pos = np.arange(max_position, dtype=np.float32)
     angle = (pos[:, None] * inv[None, :]).astype(np.float32)  # float32 multiply
     a64 = angle.astype(np.float64)
-    table = np.stack([np.cos(a64).astype(np.float32), np.sin(a64).astype(np.float32)], axis=-1)
+    table = np.stack([(np.cos(a64) * magnitude).astype(np.float32), (np.sin(a64) * magnitude).astype(np.float32)], axis=-1)
     return torch.from_numpy(np.ascontiguousarray(table))
 
 
@@ -45,6 +67,8 @@ class Rope(Position):
             raise ValueError(f"rope pairing {spec.pairing!r} is not supported ('half' or 'interleaved')")
         if spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even")
+        if getattr(spec, "rescale", None) is not None and spec.pairing != "half":
+            raise ValueError("rescaled frequencies are built into the (cos, sin) table, which only the 'half' pairing uses")
         self.rotary_dim = spec.rotary_dim
         self.pairing = spec.pairing
         self._tables = {}
@@ -60,7 +84,8 @@ class Rope(Position):
             return None
         key = str(device)
         if key not in self._tables:
-            self._tables[key] = rotary_table(self.spec.theta, self.spec.rotary_dim, self.spec.max_position).to(device)
+            self._tables[key] = rotary_table(self.spec.theta, self.spec.rotary_dim, self.spec.max_position,
+                                             getattr(self.spec, "rescale", None)).to(device)
         return self._tables[key]
 
 
