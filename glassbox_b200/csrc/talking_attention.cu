@@ -215,6 +215,414 @@ GB_EXPORT int gb_talking_attention_rows(const void* q, float* out, int dtype, co
 }
 
 // ----------------------------------------------------------------------------------------------
+// Single decoded tokens: one block of 8 warps per (row, R query heads of one key/value group). The warps take the row's
+// visible keys 32 at a time in turn (warp w the chunks w, w + 8, ...): a lane reads "its" key once and dots it with the R
+// queries; then the wide value rows of the 32 keys pass one after the other, a lane per channel, each value multiplied into
+// the R heads' sums. Every warp keeps a running maximum and a denominator per head of its own; at the end the warps meet in
+// shared memory (fixed order), where the unit of the denominator joins. The order of a row's sums depends on its position
+// and the window alone. R * NC <= 32 (NC = 32-channel pieces of the wide value row).
+// ----------------------------------------------------------------------------------------------
+constexpr int TKD_WARPS = 8;
+
+template <typename T, int R, int NC>
+__global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kernel(
+    const T* __restrict__ q, float* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+    const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
+    int n, int H, int G, int D, int V, int VG, int page_size, long long num_pages, float scale, float cap, float unit, int window,
+    int* __restrict__ status) {
+    __shared__ float qs[R * SA_MAX_DIM];
+    __shared__ float part[TKD_WARPS][R][NC * 32 + 2];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x, head0 = blockIdx.y * R;
+    if (row >= n) return;
+    const int g = head0 / (H / G);
+    const int pos = positions[row];
+    if (pos < 0) return;
+    if (pos / page_size >= max_pages) {
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int* table = block_tables + (size_t)row_seq[row] * max_pages;
+    for (int i = threadIdx.x; i < R * D; i += TKD_WARPS * 32) qs[i] = gb_to_float(q[((size_t)row * H + head0) * D + i]);
+    __syncthreads();
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int wide = VG * V;
+    float m[R], l[R], acc[R][NC];
+    int voff[NC];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) acc[r][j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+        const int i = lane + 32 * j;
+        const int c = VG == 1 ? g : i / V;
+        voff[j] = i < wide ? c * page_size * V + i % V : -1;
+    }
+    for (int base = first + warp * 32; base <= pos; base += TKD_WARPS * 32) {
+        const int key = base + lane;
+        float s[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] = -INFINITY;
+        long long at = -1;
+        if (key <= pos) {
+            const long long page = table[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                atomicOr(status, GB_STATUS_BAD_SLOT);
+            } else {
+                at = page * G * page_size + key % page_size;
+                sad_dots<T, R>(qs, kcache + (at + (long long)g * page_size) * D, D, s);
+#pragma unroll
+                for (int r = 0; r < R; ++r) s[r] = tk_cap(s[r] * scale, cap, inv_cap);
+            }
+        }
+        float p[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float m_new = fmaxf(m[r], gb_warp_max(s[r]));
+            const float corr = m_new == -INFINITY ? 1.f : expf(m[r] - m_new);
+            p[r] = at >= 0 ? expf(s[r] - m_new) : 0.f;
+            l[r] = l[r] * corr + gb_warp_sum(p[r]);
+            m[r] = m_new;
+#pragma unroll
+            for (int j = 0; j < NC; ++j) acc[r][j] *= corr;
+        }
+        const int count = min(32, pos - base + 1);
+        for (int t = 0; t < count; ++t) {
+            const long long vr = __shfl_sync(0xffffffffu, at, t);
+            float pt[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) pt[r] = __shfl_sync(0xffffffffu, p[r], t);
+            if (vr < 0) continue;
+            const T* vp = vcache + vr * V;
+            float val[NC];
+#pragma unroll
+            for (int j = 0; j < NC; ++j) val[j] = voff[j] >= 0 ? gb_to_float(vp[voff[j]]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int j = 0; j < NC; ++j) acc[r][j] = fmaf(pt[r], val[j], acc[r][j]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int j = 0; j < NC; ++j) part[warp][r][lane + 32 * j] = acc[r][j];
+        if (lane == 0) {
+            part[warp][r][NC * 32] = m[r];
+            part[warp][r][NC * 32 + 1] = l[r];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < R * wide; idx += TKD_WARPS * 32) {
+        const int r = idx / wide, i = idx % wide;
+        float top = unit > 0.f ? 0.f : -INFINITY;
+#pragma unroll
+        for (int w = 0; w < TKD_WARPS; ++w) top = fmaxf(top, part[w][r][NC * 32]);
+        float den = unit > 0.f ? unit * expf(-top) : 0.f, sum = 0.f;
+        if (top > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < TKD_WARPS; ++w) {
+                const float mw = part[w][r][NC * 32];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - top);
+                den = fmaf(part[w][r][NC * 32 + 1], f, den);
+                sum = fmaf(part[w][r][i], f, sum);
+            }
+        }
+        out[((size_t)row * H + head0 + r) * wide + i] = den > 0.f ? sum / den : 0.f;
+    }
+}
+
+GB_EXPORT int gb_talking_attention_decode_plan(int H, int G, int V, int VG) {
+    // heads per block: the largest of 8, 4, 2, 1 that divides the group and keeps R * NC within 32; 0: no kernel
+    const int wide = VG * V;
+    int nc = 1;
+    while (nc < 8 && nc * 32 < wide) nc *= 2;
+    if (nc * 32 < wide) nc = wide <= 384 ? 12 : 16;
+    if (nc * 32 < wide) return 0;
+    for (int r = 8; r >= 1; r /= 2)
+        if ((H / G) % r == 0 && r * nc <= 32) return r * 100 + nc;
+    return 0;
+}
+
+GB_EXPORT int gb_talking_attention_decode(const void* q, float* out, int dtype, const void* kcache, const void* vcache,
+                                          const int* block_tables, int max_pages, const int* row_seq, const int* positions, int n, int H,
+                                          int G, int D, int V, int VG, int page_size, long long num_pages, float scale, float cap,
+                                          float unit, int window, int* status, cudaStream_t stream) {
+    TK_COMMON_CHECKS("gb_talking_attention_decode")
+    const int plan = gb_talking_attention_decode_plan(H, G, V, VG);
+    GB_REQUIRE(plan > 0, "gb_talking_attention_decode: %d value heads of %d channels are not built", VG, V);
+    if (n == 0) return 0;
+    const int R = plan / 100, nc = plan % 100;
+    const dim3 grid(n, H / R);
+#define TKD_LAUNCH(T, RR, N)                                                                                                               gb_launch(GB_PDL_ATTENTION, talking_attention_decode_kernel<T, RR, N>, grid, dim3(TKD_WARPS * 32), 0, stream, (const T*)q, out,                   (const T*)kcache, (const T*)vcache, block_tables, max_pages, row_seq, positions, n, H, G, D, V, VG, page_size, num_pages,               scale, cap, unit, window, status)
+#define TKD_CASE(T, RR, N) if (R == RR && nc == N) { TKD_LAUNCH(T, RR, N); launched = true; }
+#define TKD_ALL(T)                                                                                                                          TKD_CASE(T, 1, 1) TKD_CASE(T, 1, 2) TKD_CASE(T, 1, 4) TKD_CASE(T, 1, 8) TKD_CASE(T, 1, 12) TKD_CASE(T, 1, 16)                           TKD_CASE(T, 2, 1) TKD_CASE(T, 2, 2) TKD_CASE(T, 2, 4) TKD_CASE(T, 2, 8) TKD_CASE(T, 2, 12) TKD_CASE(T, 2, 16)                           TKD_CASE(T, 4, 1) TKD_CASE(T, 4, 2) TKD_CASE(T, 4, 4) TKD_CASE(T, 4, 8)                                                                TKD_CASE(T, 8, 1) TKD_CASE(T, 8, 2) TKD_CASE(T, 8, 4)
+    bool launched = false;
+    if (dtype == GB_F32) { TKD_ALL(float) }
+    else if (dtype == GB_BF16) { TKD_ALL(__nv_bfloat16) }
+    else GB_REQUIRE(false, "gb_talking_attention_decode: unsupported dtype %d", dtype);
+#undef TKD_ALL
+#undef TKD_CASE
+#undef TKD_LAUNCH
+    GB_REQUIRE(launched, "gb_talking_attention_decode: no kernel for %d heads a block and %d pieces", R, nc);
+    return gb_check_launch("gb_talking_attention_decode");
+}
+
+// ----------------------------------------------------------------------------------------------
+// Prompt portions in bfloat16 on the tensor cores. One block = 64 rows of one request x one query head x VC columns of the
+// wide value row (the values of all key/value heads side by side; blockIdx.z picks the columns, and every such block forms
+// the head's scores again). The keys any row of the tile can see pass in 64-key tiles through shared memory (cp.async, two
+// buffers, pages through the block table); S = Q K^T and O += P V with mma.sync m16n8k16, P from the score fragments in
+// registers, float32 online softmax in the base-2 domain whose maximum starts at the unit's score (0). Four warps, 16 rows
+// each. The float32 results go to out[row, head, z * VC ..].
+// ----------------------------------------------------------------------------------------------
+constexpr int TKT_BM = 64, TKT_BN = 64;
+constexpr float TK_LOG2E = 1.4426950408889634f;
+
+template <int D, int VC>
+__global__ void __launch_bounds__(128) talking_attention_tiles_kernel(
+    const __nv_bfloat16* __restrict__ q, float* __restrict__ out, const __nv_bfloat16* __restrict__ kcache,
+    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_first_row,
+    const int* __restrict__ seq_start_pos, int num_seqs, int tiles_per_seq, int H, int G, int V, int VG, int page_size,
+    long long num_pages, float scale, float cap, float unit, int window, int* __restrict__ status) {
+    constexpr int LDK = D + 8, LDV = VC + 8;          // rows padded by 16 bytes: ldmatrix meets no bank twice
+    extern __shared__ __align__(16) unsigned char tkt_smem[];
+    __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(tkt_smem);             // [64][LDK]
+    __nv_bfloat16* sk = sq + TKT_BM * LDK;                                        // [2][64][LDK]
+    __nv_bfloat16* sv = sk + 2 * TKT_BN * LDK;                                    // [2][64][LDV]
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x / tiles_per_seq, tile = blockIdx.x % tiles_per_seq, head = blockIdx.y, col0 = blockIdx.z * VC;
+    if (seq >= num_seqs) return;
+    const int start = seq_start_pos[seq];
+    if (start < 0) return;
+    const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
+    if (tile * TKT_BM >= len) return;
+    const int rows = min(TKT_BM, len - tile * TKT_BM);
+    const int row0 = r0 + tile * TKT_BM, p_lo = start + tile * TKT_BM, p_hi = p_lo + rows - 1;
+    if (p_hi / page_size >= max_pages) {
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int k_lo = (window > 0 && p_lo + 1 > window) ? p_lo + 1 - window : 0;
+    const int g = head / (H / G);
+    const int wide = VG * V;
+    const int* table = block_tables + (size_t)seq * max_pages;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int chunk = tid; chunk < TKT_BM * (D / 8); chunk += 128) {
+        const int r = chunk / (D / 8), c = (chunk % (D / 8)) * 8;
+        sat_cp16(sq + r * LDK + c, q + ((size_t)(row0 + (r < rows ? r : 0)) * H + head) * D + c, r < rows);
+    }
+    auto stage = [&](int buf, int kb) {
+        // two threads per key: one page look-up each, then half of the key's 16-byte pieces (key row, then the value columns)
+        constexpr int CPK = (D + VC) / 8;
+        const int key = tid >> 1, kk = kb + key;
+        long long page = kk <= p_hi ? table[kk / page_size] : -1;
+        if (kk <= p_hi && (page < 0 || page >= num_pages)) {
+            atomicOr(status, GB_STATUS_BAD_SLOT);
+            page = -1;
+        }
+        const long long at = page < 0 ? 0 : page * G * page_size + kk % page_size;
+#pragma unroll
+        for (int i = 0; i < CPK / 2; ++i) {
+            const int c = ((tid & 1) * (CPK / 2) + i) * 8;
+            if (c < D) {
+                sat_cp16(sk + (buf * TKT_BN + key) * LDK + c, kcache + (at + (long long)g * page_size) * D + c, page >= 0);
+            } else {
+                const int w = col0 + (c - D);                           // column of the wide value row
+                const int vh = VG == 1 ? g : w / V;
+                sat_cp16(sv + (buf * TKT_BN + key) * LDV + (c - D), vcache + (at + (long long)vh * page_size) * V + w % V, page >= 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (p_hi - k_lo) / TKT_BN + 1;
+    stage(0, k_lo);                                   // (one group holds Q and the first keys)
+    unsigned qf[D / 16][4];
+    float o[VC / 8][4];
+#pragma unroll
+    for (int j = 0; j < VC / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const float unit2 = unit > 0.f ? 0.f : -INFINITY;                                 // the unit's score, 0, in the base-2 domain
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f, cap2 = cap * TK_LOG2E, scale2 = scale * TK_LOG2E;
+    const int my_pos0 = p_lo + warp * 16 + (lane >> 2), my_pos1 = my_pos0 + 8;       // positions of this thread's two rows
+    float mrow[2] = {unit2, unit2}, lrow[2] = {0.f, 0.f};                             // (a thread's share of the denominator)
+    for (int t = 0; t < n_tiles; ++t) {
+        const int kb = k_lo + t * TKT_BN, buf = t & 1;
+        if (t + 1 < n_tiles) {
+            stage(buf ^ 1, kb + TKT_BN);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        if (t == 0) {
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(sq + (warp * 16 + (lane & 15)) * LDK + kd * 16 + (lane >> 4) * 8);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(qf[kd][0]), "=r"(qf[kd][1]), "=r"(qf[kd][2]), "=r"(qf[kd][3]) : "r"(addr));
+            }
+        }
+        // a warp whose rows lie wholly before this tile's first key or (with a window) wholly behind its last visible one
+        // still walks the barriers, but skips the arithmetic
+        const int w_lo = p_lo + warp * 16, w_hi = w_lo + 15;
+        const bool any = kb <= w_hi && (window <= 0 || kb + TKT_BN - 1 > w_lo - window) && warp * 16 < rows;
+        if (any) {
+            float s[TKT_BN / 8][4];
+#pragma unroll
+            for (int j = 0; j < TKT_BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            const __nv_bfloat16* kt = sk + buf * TKT_BN * LDK;
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+#pragma unroll
+                for (int j2 = 0; j2 < TKT_BN / 16; ++j2) {
+                    unsigned b0, b1_, b2_, b3;
+                    const int nrow = j2 * 16 + (lane & 7) + ((lane >> 4) << 3), kcol = kd * 16 + ((lane >> 3) & 1) * 8;
+                    const unsigned addr = (unsigned)__cvta_generic_to_shared(kt + nrow * LDK + kcol);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1_), "=r"(b2_), "=r"(b3) : "r"(addr));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(s[2 * j2][0]), "+f"(s[2 * j2][1]), "+f"(s[2 * j2][2]), "+f"(s[2 * j2][3])
+                                 : "r"(qf[kd][0]), "r"(qf[kd][1]), "r"(qf[kd][2]), "r"(qf[kd][3]), "r"(b0), "r"(b1_));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(s[2 * j2 + 1][0]), "+f"(s[2 * j2 + 1][1]), "+f"(s[2 * j2 + 1][2]), "+f"(s[2 * j2 + 1][3])
+                                 : "r"(qf[kd][0]), "r"(qf[kd][1]), "r"(qf[kd][2]), "r"(qf[kd][3]), "r"(b2_), "r"(b3));
+                }
+            }
+            // capped scores in the base-2 domain; the causal edge and the window per element, except in tiles that every row
+            // of the warp sees whole (most of them); then the rows' maxima (a row lies in the four lanes of a quad)
+            const bool whole = kb + TKT_BN - 1 <= w_lo && (window <= 0 || w_hi - kb < window) && w_hi <= p_hi;
+            float mx[2] = {mrow[0], mrow[1]};
+#pragma unroll
+            for (int j = 0; j < TKT_BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = e < 2 ? my_pos0 : my_pos1;
+                    float v = cap > 0.f ? cap2 * tanhf(s[j][e] * scale * inv_cap) : s[j][e] * scale2;
+                    if (!whole) {
+                        const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
+                        v = sees ? v : -INFINITY;
+                    }
+                    s[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 1));
+                mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 2));
+                corr[hrow] = mx[hrow] == -INFINITY ? 1.f : exp2f(mrow[hrow] - mx[hrow]);
+                mrow[hrow] = mx[hrow];
+                lrow[hrow] *= corr[hrow];
+            }
+            const float sub0 = mx[0] == -INFINITY ? 0.f : mx[0], sub1 = mx[1] == -INFINITY ? 0.f : mx[1];
+#pragma unroll
+            for (int j = 0; j < VC / 8; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            unsigned pf[TKT_BN / 16][4];
+#pragma unroll
+            for (int j = 0; j < TKT_BN / 8; ++j) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) p[e] = exp2f(s[j][e] - (e < 2 ? sub0 : sub1));
+                // the denominator sums what the products use: the weights as rounded to bfloat16
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+                const float2 flo = __bfloat1622float2(lo), fhi = __bfloat1622float2(hi);
+                lrow[0] += flo.x + flo.y;
+                lrow[1] += fhi.x + fhi.y;
+                pf[j >> 1][(j & 1) * 2] = *reinterpret_cast<const unsigned*>(&lo);
+                pf[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const unsigned*>(&hi);
+            }
+            const __nv_bfloat16* vt = sv + buf * TKT_BN * LDV;
+#pragma unroll
+            for (int kk = 0; kk < TKT_BN / 16; ++kk) {
+#pragma unroll
+                for (int n2 = 0; n2 < VC / 16; ++n2) {
+                    unsigned b0, b1_, b2_, b3;
+                    const int krow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ncol = n2 * 16 + (lane >> 4) * 8;
+                    const unsigned addr = (unsigned)__cvta_generic_to_shared(vt + krow * LDV + ncol);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1_), "=r"(b2_), "=r"(b3) : "r"(addr));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(o[2 * n2][0]), "+f"(o[2 * n2][1]), "+f"(o[2 * n2][2]), "+f"(o[2 * n2][3])
+                                 : "r"(pf[kk][0]), "r"(pf[kk][1]), "r"(pf[kk][2]), "r"(pf[kk][3]), "r"(b0), "r"(b1_));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(o[2 * n2 + 1][0]), "+f"(o[2 * n2 + 1][1]), "+f"(o[2 * n2 + 1][2]), "+f"(o[2 * n2 + 1][3])
+                                 : "r"(pf[kk][0]), "r"(pf[kk][1]), "r"(pf[kk][2]), "r"(pf[kk][3]), "r"(b2_), "r"(b3));
+                }
+            }
+        }
+        __syncthreads();          // everyone is done with this buffer before the round after next overwrites it
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float den = lrow[half];
+        den += __shfl_xor_sync(0xffffffffu, den, 1);
+        den += __shfl_xor_sync(0xffffffffu, den, 2);
+        if (unit > 0.f) den += unit * exp2f(unit2 - mrow[half]);          // (the maximum started at the unit's score: at most 1)
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        if (r >= rows) continue;
+        const float f = den > 0.f ? 1.0f / den : 0.f;
+        float* dst = out + ((size_t)(row0 + r) * H + head) * wide + col0;
+#pragma unroll
+        for (int j = 0; j < VC / 8; ++j)
+            *reinterpret_cast<float2*>(dst + j * 8 + (lane & 3) * 2) = make_float2(o[j][half * 2] * f, o[j][half * 2 + 1] * f);
+    }
+}
+
+// the columns of the wide value row that one block takes: the largest of 128, 64, 32 that divides the row; 0: no kernel
+GB_EXPORT int gb_talking_attention_tiles_columns(int D, int V, int VG) {
+    if (!(D == 32 || D == 64 || D == 96 || D == 128) || V % 8) return 0;
+    const int wide = VG * V;
+    for (int vc = 128; vc >= 32; vc /= 2)
+        if (wide % vc == 0) return vc;
+    return 0;
+}
+
+template <int D, int VC>
+static int tkt_launch(const void* q, float* out, const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                      const int* seq_first_row, const int* seq_start_pos, int num_seqs, int tiles_per_seq, int H, int G, int V, int VG,
+                      int page_size, long long num_pages, float scale, float cap, float unit, int window, int* status,
+                      cudaStream_t stream) {
+    const size_t smem = ((size_t)3 * TKT_BM * (D + 8) + (size_t)2 * TKT_BN * (VC + 8)) * 2;
+    cudaFuncSetAttribute(talking_attention_tiles_kernel<D, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gb_launch(GB_PDL_ATTENTION, talking_attention_tiles_kernel<D, VC>, dim3(num_seqs * tiles_per_seq, H, VG * V / VC), dim3(128), smem,
+              stream, (const __nv_bfloat16*)q, out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables, max_pages,
+              seq_first_row, seq_start_pos, num_seqs, tiles_per_seq, H, G, V, VG, page_size, num_pages, scale, cap, unit, window, status);
+    return gb_check_launch("gb_talking_attention_tiles");
+}
+
+GB_EXPORT int gb_talking_attention_tiles(const void* q, float* out, const void* kcache, const void* vcache, const int* block_tables,
+                                         int max_pages, const int* seq_first_row, const int* seq_start_pos, int num_seqs,
+                                         int max_rows_per_seq, int H, int G, int D, int V, int VG, int page_size, long long num_pages,
+                                         float scale, float cap, float unit, int window, int* status, cudaStream_t stream) {
+    const int n = num_seqs;
+    TK_COMMON_CHECKS("gb_talking_attention_tiles")
+    const int vc = gb_talking_attention_tiles_columns(D, V, VG);
+    GB_REQUIRE(vc > 0 && max_rows_per_seq > 0, "gb_talking_attention_tiles: head sizes %d / %d x %d are not built", D, V, VG);
+    if (num_seqs == 0) return 0;
+    const int tiles = gb_ceil_div(max_rows_per_seq, TKT_BM);
+#define TKT_CASE(DD, VV)                                                                                                             \
+    if (D == DD && vc == VV)                                                                                                          \
+        return tkt_launch<DD, VV>(q, out, kcache, vcache, block_tables, max_pages, seq_first_row, seq_start_pos, num_seqs, tiles, H, G, \
+                                  V, VG, page_size, num_pages, scale, cap, unit, window, status, stream);
+    TKT_CASE(32, 32) TKT_CASE(32, 64) TKT_CASE(32, 128) TKT_CASE(64, 32) TKT_CASE(64, 64) TKT_CASE(64, 128) TKT_CASE(96, 32)
+    TKT_CASE(96, 64) TKT_CASE(96, 128) TKT_CASE(128, 32) TKT_CASE(128, 64) TKT_CASE(128, 128)
+#undef TKT_CASE
+    GB_REQUIRE(false, "gb_talking_attention_tiles: head sizes %d / %d are not built", D, vc);
+}
+
+// ----------------------------------------------------------------------------------------------
 // The mix: att[row, h, :] = sum_g talk[h, g] * O[row, g, c(h), :] (talk == nullptr: O[row, h, c(h) or 0, :] as it is).
 // One thread per (row, h, channel).
 // ----------------------------------------------------------------------------------------------

@@ -104,6 +104,10 @@ _SIGNATURES = {
     "gb_scaled_sum": [_P, _P, _F, _F, _P, _LL, _I, _P],
     "gb_bias_rope_write": [_P, _LL, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _LL, _I, _P, _P],
     "gb_talking_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
+    "gb_talking_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
+    "gb_talking_attention_decode_plan": [_I, _I, _I, _I],
+    "gb_talking_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
+    "gb_talking_attention_tiles_columns": [_I, _I, _I],
     "gb_talk_combine": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P],
@@ -1649,6 +1653,47 @@ def talking_attention_rows(q: torch.Tensor, wide: torch.Tensor, kcache: torch.Te
     _call("gb_talking_attention_rows", _ptr(q), _ptr(wide), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
           _ptr(row_seq), _ptr(positions), n, heads, kv_heads, dim, vdim, value_heads, page_size, kcache.shape[0], float(scale),
           float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), _ptr(status), _stream())
+
+
+def talking_attention_decode_supported(dtype: torch.dtype, heads: int, kv_heads: int, vdim: int, value_heads: int) -> bool:
+    return dtype in _DT and bool(lib().gb_talking_attention_decode_plan(heads, kv_heads, vdim, value_heads))
+
+
+def talking_attention_decode(q: torch.Tensor, wide: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                             row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                             value_heads: int, page_size: int, scale: float, softcap: Optional[float], unit_sink: bool,
+                             window: Optional[int], status: torch.Tensor) -> None:
+    """``talking_attention_rows`` for steps of single decoded tokens: a block of eight warps per (row, up to eight heads of a
+    key/value group) that take the row's keys in turn and merge in shared memory; a key row is read once for the block's heads."""
+    _cuda(q, wide, kcache, vcache, block_tables, row_seq, positions, status)
+    n = q.shape[0]
+    assert q.shape == (n, heads * dim) and q.is_contiguous() and q.dtype == kcache.dtype == vcache.dtype
+    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert block_tables.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and n <= 2 ** 31 - 1
+    _call("gb_talking_attention_decode", _ptr(q), _ptr(wide), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(row_seq), _ptr(positions), n, heads, kv_heads, dim, vdim, value_heads, page_size, kcache.shape[0], float(scale),
+          float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), _ptr(status), _stream())
+
+
+def talking_attention_tiles_supported(dtype: torch.dtype, dim: int, vdim: int, value_heads: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().gb_talking_attention_tiles_columns(dim, vdim, value_heads))
+
+
+def talking_attention_tiles(q: torch.Tensor, wide: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                            seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, max_rows_per_seq: int, heads: int, kv_heads: int,
+                            dim: int, vdim: int, value_heads: int, page_size: int, scale: float, softcap: Optional[float],
+                            unit_sink: bool, window: Optional[int], status: torch.Tensor) -> None:
+    """``talking_attention_rows`` for prompt portions in bfloat16 on the tensor cores: 64 rows of one request x one head x up to
+    128 columns of the wide value row per block."""
+    _cuda(q, wide, kcache, vcache, block_tables, seq_first_row, seq_start_pos, status)
+    n = q.shape[0]
+    assert q.dtype == kcache.dtype == vcache.dtype == torch.bfloat16 and q.shape == (n, heads * dim) and q.is_contiguous()
+    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert block_tables.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous()
+    _call("gb_talking_attention_tiles", _ptr(q), _ptr(wide), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(seq_first_row), _ptr(seq_start_pos), seq_start_pos.shape[0], int(max_rows_per_seq), heads, kv_heads, dim, vdim, value_heads,
+          page_size, kcache.shape[0], float(scale), float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), _ptr(status),
+          _stream())
 
 
 def talk_combine(wide: torch.Tensor, talk: Optional[torch.Tensor], att: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int,

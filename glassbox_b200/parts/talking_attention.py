@@ -23,6 +23,17 @@ from .base import Mixer, PagedKvSpec, build_part, register_part
 from .linear import linear
 
 
+def pick_kernel(dtype, single_tokens: bool, heads: int, kv_heads: int, dim: int, vdim: int, value_heads: int) -> str:
+    """Which attention kernel a step takes: "decode" (single decoded tokens, a block of warps per (row, head) that share the
+    row's keys), "tiles" (prompt portions in bfloat16 on the tensor cores) or "rows" (one warp per (row, head): float32
+    portions, sizes the others are not built for)."""
+    if single_tokens and kernels.talking_attention_decode_supported(dtype, heads, kv_heads, vdim, value_heads):
+        return "decode"
+    if not single_tokens and kernels.talking_attention_tiles_supported(dtype, dim, vdim, value_heads):
+        return "tiles"
+    return "rows"
+
+
 class TalkingAttention(Mixer):
     accepts_deferred_input = True
     launches_through_kernels_only = True
@@ -84,7 +95,14 @@ class TalkingAttention(Mixer):
         s = self.spec
         common = dict(heads=self.H, kv_heads=self.G, dim=self.D, vdim=self.V, value_heads=value_heads, page_size=cache.page_size,
                       scale=s.scale, softcap=s.softcap, unit_sink=s.unit_sink, window=s.window, status=ctx.status)
-        kernels.talking_attention_rows(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
+        how = pick_kernel(q.dtype, ctx.decode_only, self.H, self.G, self.D, self.V, value_heads)
+        if how == "decode":
+            kernels.talking_attention_decode(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
+        elif how == "tiles":
+            kernels.talking_attention_tiles(q, wide, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,
+                                            ctx.max_rows_per_seq, **common)
+        else:
+            kernels.talking_attention_rows(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
 
 
 register_part("mixer", "talking_attention", TalkingAttention, replace=True)

@@ -106,18 +106,20 @@ def talking_softmax_attention(h, W, p, m):
     """Causal grouped-query attention: biased projections, rotation, capped scores, a softmax whose denominator holds one
     more unit (a key of score 0 without a value), the heads' weights mixed by a matrix before they meet the values."""
     T = h.shape[0]
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, D, V = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     q = (h @ W[p + "q"].T + W[p + "q.b"]).reshape(T, H, D)
     k = (h @ W[p + "k"].T + W[p + "k.b"]).reshape(T, G, D)
     v = (h @ W[p + "v"].T + W[p + "v.b"]).reshape(T, G, V)
     pos = np.arange(T)
-    q, k = rotate_half(q, pos, m["rot"]), rotate_half(k, pos, m["rot"])
+    if m.get("rot") is not None:
+        q, k = rotate_half(q, pos, m["rot"]), rotate_half(k, pos, m["rot"])
     weights = np.zeros((H, T, T))
     for head in range(H):
         g = head // (H // G)
         for i in range(T):
             s = np.array([q[i, head] @ k[j, g] * m["scale"] for j in range(i + 1)])
-            s = m["softcap"] * np.tanh(s / m["softcap"])
+            if m.get("softcap") is not None:
+                s = m["softcap"] * np.tanh(s / m["softcap"])
             e = np.exp(s)
             weights[head, i, :i + 1] = e / (1.0 + e.sum())
     mixed = np.einsum("hg,gij->hij", W[p + "talk"], weights)
@@ -130,7 +132,7 @@ def talking_softmax_attention(h, W, p, m):
 def gated_delta(h, W, p, m, eps):
     """Gated delta rule with one decay per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
     T = h.shape[0]
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, D, V = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     q = silu(causal_conv(h @ W[p + "q"].T, W[p + "q.conv"])).reshape(T, G, D)
     k = silu(causal_conv(h @ W[p + "k"].T, W[p + "k.conv"])).reshape(T, G, D)
     v = silu(causal_conv(h @ W[p + "v"].T, W[p + "v.conv"])).reshape(T, H, V)
@@ -153,8 +155,8 @@ def gated_delta(h, W, p, m, eps):
 
 
 def parallel(h, W, p, m, eps):
-    return (m["left_scale"] * talking_softmax_attention(h, W, p + "left.", m["left"])
-            + m["right_scale"] * gated_delta(h, W, p + "right.", m["right"], eps))
+    return (m.get("left_scale", 1.0) * talking_softmax_attention(h, W, p + "left.", m["left"])
+            + m.get("right_scale", 1.0) * gated_delta(h, W, p + "right.", m["right"], eps))
 
 
 def dense_ff(h, W, p):
