@@ -540,6 +540,54 @@ def tagenex_workload(args):
     return out
 
 
+# ------------------------------------------------------------------------------------------------ Babotar beside its neighbours
+#: layer sizes that resemble real models' (random weights): a Babotar model whose layers alternate between lightning attention
+#: and the pair of talking-heads attention and gated delta rule, four residual streams, a convolution of four taps on every
+#: mixer's input, gated GELU feed-forwards. Beside it Zurerax (the framework's other model of delta-rule and attention layers)
+#: and the Llama decoder, both of the same width, depth and feed-forward width.
+BABOTAR_SIZES = {
+    "w1024": dict(lightning=dict(heads=8, dim=128, vdim=128), left=dict(heads=16, kv_heads=4, dim=64, vdim=64),
+                  right=dict(heads=4, kv_heads=4, dim=128, vdim=128, conv=4)),
+    "w2048": dict(lightning=dict(heads=16, dim=128, vdim=128), left=dict(heads=32, kv_heads=8, dim=64, vdim=64),
+                  right=dict(heads=8, kv_heads=8, dim=128, vdim=128, conv=4)),
+}
+
+
+def babotar_raw(size: dict, own: dict, max_positions: int = 8192) -> dict:
+    from glassbox_b200.models.babotar import make_babotar_raw_config
+    layers = []
+    for i in range(size["layers"]):
+        mlp = {"kind": "dense", "ff": size["ff"]}
+        if i % 2:
+            lf = dict(own["left"])
+            lf.update(scale=lf["dim"] ** -0.5, softcap=50.0,
+                      rot={"base": 10000.0, "dims": lf["dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
+            layers.append({"type": "parallel", "mixer": {"left": lf, "right": dict(own["right"]), "left_scale": 0.6, "right_scale": 0.9},
+                           "mlp": mlp})
+        else:
+            m = dict(own["lightning"])
+            m["decay"] = [1.0 - 2.0 ** -(3 + 5 * h / max(m["heads"] - 1, 1)) for h in range(m["heads"])]
+            layers.append({"type": "lightning", "mixer": m, "mlp": mlp})
+    return make_babotar_raw_config(vocab=size["vocab"], width=size["width"], max_positions=max_positions, layers=layers, streams=4,
+                                   residual_mult=0.7, canon_taps=4)
+
+
+def babotar_workload(args):
+    """Prefill and decode throughput of Babotar models beside Zurerax and the Llama decoder of equal width, depth and
+    feed-forward width; one JSON line. Decode steps end at the context length; three timed regions per point."""
+    T, ctx, K, W = 2048, args.context, min(args.steps, 128), max(args.warmup, 3)
+    out = {"workload": "babotar", "dtype": args.dtype, "context": ctx, "prefill_tokens": T, "decode_steps": K, "sizes": {}}
+    for name, size in ZURERAX_SIZES.items():
+        llama = dict(num_hidden_layers=size["layers"], hidden_size=size["width"], intermediate_size=size["ff"],
+                     vocab_size=size["vocab"], rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                     max_position_embeddings=8192, **size["llama"])
+        arms = (("babotar", dict(raw=babotar_raw(size, BABOTAR_SIZES[name], max(8192, ctx)))), ("zurerax", dict(raw=zurerax_raw(size))),
+                ("llama", dict(shape=llama)))
+        out["sizes"][name] = {label: measure_arm(f"{label}-{name}", args, T, ctx, K, W, **kw) for label, kw in arms
+                              if not args.only or label in args.only.split(",")}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -554,14 +602,14 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="only the headline region: no other batches, prefill or e2e")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the other model sizes, the serving workload, the 32-bit path and the CPU baseline")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax", "lonorax", "tagenex"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax", "lonorax", "tagenex", "babotar"],
                     help="serving: the mixed workload of the 360M configuration (64 requests, prompts 32-2048, outputs "
                          "32-512, prompt portions of 512, a quarter of the requests sharing a 384-token prefix) through "
                          "the scheduler; prints its own JSON line. zurerax: prefill and decode throughput of Zurerax models "
                          "at two widths beside the Llama decoder of equal size; prints its own JSON line. lonorax: the same for "
                          "Lonorax models beside Zurerax and Llama of equal size; tagenex: the same for Tagenex models beside Llama "
-                         "and Lonorax of equal size")
-    ap.add_argument("--only", default="", help="with --workload lonorax or tagenex: the arms to run (tagenex,lonorax,zurerax,llama), with commas")
+                         "and Lonorax of equal size; babotar: the same for Babotar models beside Zurerax and Llama of equal size")
+    ap.add_argument("--only", default="", help="with --workload lonorax, tagenex or babotar: the arms to run (babotar,tagenex,lonorax,zurerax,llama), with commas")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -585,6 +633,9 @@ def main():
         return 0
     if args.workload == "tagenex":
         print(json.dumps(tagenex_workload(args)))
+        return 0
+    if args.workload == "babotar":
+        print(json.dumps(babotar_workload(args)))
         return 0
     K, W, B, CTX = args.steps, max(args.warmup, 3), args.batch, args.context
     pk = peaks()

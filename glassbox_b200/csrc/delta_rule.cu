@@ -131,7 +131,8 @@ struct ChannelDeltaArgs {
 // CD_PLAIN: linear attention with a fixed decay per head, S <- decay_h S + k v^T, o = S^T q: no beta, no correction towards
 //           the value, no unit vectors, no factor on q; `a_log` then holds the decays themselves, a, beta and dt_bias are not read.
 // CD_GATE_SILU: the decoding form's output gate is silu(gate) instead of sigmoid(gate).
-enum { CD_SILU_INPUTS = 1, CD_PLAIN = 2, CD_GATE_SILU = 4 };
+// CD_NO_NORM: the decoding form leaves the read-out as it is (float32, no norm, no gate), for a norm that spans the heads.
+enum { CD_SILU_INPUTS = 1, CD_PLAIN = 2, CD_GATE_SILU = 4, CD_NO_NORM = 8 };
 __device__ __forceinline__ float cd_silu(float v) { return v / (1.0f + expf(-v)); }
 
 template <int DPT, int NS>
@@ -464,6 +465,7 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
     }
     const size_t row = (size_t)p.seq_first_row[seq];
     const int dk = p.dk, dv = p.dv;
+    const bool plain = p.flags & CD_PLAIN, silu_in = p.flags & CD_SILU_INPUTS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int kvh = head / (p.heads / p.kv_heads);
     float* sbase = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * dv;
@@ -499,20 +501,22 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
             const size_t ai = (size_t)head * p.decay_channels + (p.decay_channels > 1 ? tid : 0);
             qv = p.qkv[row * p.ldq + (size_t)kvh * dk + tid];
             kv = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + tid];
-            zv = p.a[row * p.lda + ai] + p.dt_bias[ai];
+            if (!plain) zv = p.a[row * p.lda + ai] + p.dt_bias[ai];
+            if (silu_in) { qv = cd_silu(qv); kv = cd_silu(kv); }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int col = lane + 32 * c;
             vt[c] = col < dv ? p.qkv[row * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + col] : 0.f;
+            if (silu_in) vt[c] = cd_silu(vt[c]);
         }
     }
-    const float beta = 1.0f / (1.0f + __expf(-p.beta[row * p.ldb + head]));
+    const float beta = plain ? 1.0f : 1.0f / (1.0f + __expf(-p.beta[row * p.ldb + head]));
     if (tid < 128) {
         const float sp = zv > 15.f ? zv : __logf(1.0f + __expf(zv));
         qs[tid] = qv;
         ks[tid] = kv;
-        gs[tid] = __expf(-expf(p.a_log[head]) * sp);
+        gs[tid] = plain ? (tid < dk ? p.a_log[head] : 1.0f) : __expf(-expf(p.a_log[head]) * sp);
         const float sq = gb_warp_sum(qv * qv), sk = gb_warp_sum(kv * kv);
         if (lane == 0) { red[warp] = sq; red[4 + warp] = sk; }
     }
@@ -521,8 +525,9 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
 #pragma unroll
         for (int c = 0; c < 4; ++c) vt[c] = lane + 32 * c < dv ? vsm[lane + 32 * c] : 0.f;
     }
-    const float iq = 1.0f / sqrtf((float)dk) / sqrtf(red[0] + red[1] + red[2] + red[3] + CD_UNIT_EPS);
-    const float ik = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + CD_UNIT_EPS);
+    const float iq = plain ? 1.0f : 1.0f / sqrtf((float)dk) / sqrtf(red[0] + red[1] + red[2] + red[3] + CD_UNIT_EPS);
+    const float ik = plain ? 1.0f : 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + CD_UNIT_EPS);
+    const float corr = plain ? 0.f : 1.f;               // how much of S^T k is taken off the value
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -543,7 +548,7 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
         float sk = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) sk += part[w][col];
-        u[c] = beta * (vt[c] - ik * sk) * ik;
+        u[c] = beta * (vt[c] - corr * ik * sk) * ik;
         acc[c] = 0.f;
     }
     __syncthreads();           // everyone has read the first sums before the second ones overwrite them
@@ -580,7 +585,9 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
         if (lane == 0) red[8 + warp] = ss;
     }
     __syncthreads();
-    if (tid < dv) {
+    if (p.flags & CD_NO_NORM) {
+        if (tid < dv) p.out[row * p.heads * dv + (size_t)head * dv + tid] = ovec[tid];
+    } else if (tid < dv) {
         const float s = 1.0f / sqrtf((red[8] + red[9] + red[10] + red[11]) / (float)dv + eps);
         const float gl = FUSED ? gsm[tid] : gate[row * ldg + (size_t)head * dv + tid];
         const float sig = (p.flags & CD_GATE_SILU) ? cd_silu(gl) : 1.0f / (1.0f + expf(-gl));
@@ -602,9 +609,10 @@ GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const flo
                                       const float* proj, long long ldp, const float* conv_w, long long conv_state_off, int taps,
                                       int a1_at, int ra, int rg, const void* w_a2, const void* w_g2, int w_dtype,
                                       int decay_channels, int flags, cudaStream_t stream) {
-    GB_REQUIRE((decay_channels == 1 || decay_channels == dk) && !(flags & (CD_PLAIN | CD_SILU_INPUTS)),
-               "gb_channel_delta_decode: %d decays per head, flags %d are not taken", decay_channels, flags);
-    GB_REQUIRE(proj == nullptr || decay_channels == dk, "gb_channel_delta_decode: the fused form wants a decay per key channel");
+    GB_REQUIRE(decay_channels == 1 || decay_channels == dk, "gb_channel_delta_decode: %d decays per head", decay_channels);
+    GB_REQUIRE(proj == nullptr || (decay_channels == dk && flags == 0), "gb_channel_delta_decode: the fused form wants a decay per key "
+               "channel and no flags");
+    GB_REQUIRE(!(flags & CD_NO_NORM) || att_dtype == GB_F32, "gb_channel_delta_decode: a read-out without its norm is float32");
     GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta_decode: heads %d must be a multiple of "
                "key heads %d", heads, kv_heads);
     GB_REQUIRE(gb_channel_delta_decode_supported(dk, dv), "gb_channel_delta_decode: key size %d and value size %d must be at most 128", dk, dv);
@@ -614,6 +622,7 @@ GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const flo
     if (S == 0) return 0;
     ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, nullptr, seq_first_row, seq_start_pos,
                           seq_slots, heads, kv_heads, dk, dv, 0, 0, num_slots, write_state, status, decay_channels, flags};
+    if (flags & CD_NO_NORM) p.out = (float*)att;
     DeltaDecodeFusion f = {proj, ldp, conv_w, conv_state_off, taps, 2 * kv_heads * dk + heads * dv, a1_at, ra, rg, w_a2, w_g2};
     dim3 grid(S, heads);
 #define CDD_LAUNCH(T, TW, F) gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<T, TW, F>, grid, dim3(256), 0, stream, p, gate, ldg, \

@@ -43,7 +43,8 @@ struct StreamArgs {
     long long prefetch_bytes;
     int late_release;         // let the next kernel in the stream go only after this one's own wait (else at its start)
     // the clamped gated unit (WS_UNIT_BF16): g = min(gate sum + bias[n], limit), u = clamp(up sum + bias[N + n], -limit, limit),
-    // c = bfloat16(g * sigmoid(slope * g) * (u + 1)); unit_bias float32 [2 N] or nullptr
+    // c = bfloat16(g * sigmoid(slope * g) * (u + 1)); unit_bias float32 [2 N] or nullptr. A negative slope selects the GELU
+    // unit instead: c = bfloat16(gelu_tanh(gate sum + bias) * (up sum + bias))
     const float* unit_bias;
     float unit_limit, unit_slope;
 };
@@ -464,7 +465,8 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             const float g = fminf(v[0] + bg, a.unit_limit);
             const float u = fminf(fmaxf(v[1] + bu, -a.unit_limit), a.unit_limit);
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] =
-                __float2bfloat16_rn(g / (1.0f + __expf(-a.unit_slope * g)) * (u + 1.0f));
+                a.unit_slope < 0.f ? __float2bfloat16_rn(gb_gelu_tanh(v[0] + bg) * (v[1] + bu))      // the GELU unit, nothing clamped
+                                   : __float2bfloat16_rn(g / (1.0f + __expf(-a.unit_slope * g)) * (u + 1.0f));
         } else if (a.mode == WS_STORE_BF16) {
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(v[0]);
         } else if (a.mode == WS_RELU2_BF16) {       // squared ReLU, from the float32 sum

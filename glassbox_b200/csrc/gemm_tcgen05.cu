@@ -59,7 +59,8 @@ struct TcNorm {
 
 // A GATED launch whose unit is the clamped one (limit > 0) instead of silu(gate) * up: with the float32 sums G and U of a
 // gate column and its up column, g = min(G + bias[col], limit), u = clamp(U + bias[gate_rows + col], -limit, limit) and the
-// output is g * sigmoid(slope * g) * (u + 1). bias (float32 [2 * gate_rows]) may be nullptr.
+// output is g * sigmoid(slope * g) * (u + 1). bias (float32 [2 * gate_rows]) may be nullptr. A negative slope selects
+// another unit altogether: gelu_tanh(G + bias) * (U + bias), the tanh form of GELU on the gate, nothing clamped.
 struct TcUnit {
     const float* bias;
     float limit, slope;
@@ -347,6 +348,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int j = j4 + e;
+                                if (unit.slope < 0.f) {      // the GELU unit: gelu_tanh(G) * U, nothing clamped
+                                    r[j] = __float_as_uint(gb_gelu_tanh(__uint_as_float(r[j]) + bg[e]) * (__uint_as_float(u[j]) * inv_rms + bu[e]));
+                                    continue;
+                                }
                                 const float g = fminf(__uint_as_float(r[j]) + bg[e], unit.limit);
                                 const float v = fminf(fmaxf(__uint_as_float(u[j]) * inv_rms + bu[e], -unit.limit), unit.limit);
                                 r[j] = __float_as_uint(__fdividef(g, 1.0f + __expf(-unit.slope * g)) * (v + 1.0f));

@@ -13,9 +13,9 @@
 //                          channels (channel i with channel i + rot/2, a (cos, sin) table per position), q into the query
 //                          buffer, k and v into the paged cache at each row's slot
 //   talking_attention_rows one warp per (row, head), any row, both dtypes
-//   talking_attention_decode  single decoded tokens: a block of 8 warps per (row, head), the warps take the keys in turn
+//   talking_attention_decode  single decoded tokens: a block of 8 warps per (row, heads of a group, share of the keys)
 //   talking_attention_tiles   prompt portions in bfloat16 on the tensor cores (mma.sync), 64 rows x one head per block
-//   talk_combine           the mix of the heads' results
+//   talk_combine           the mix of the heads' results (and the merge of the shares of the keys, if there are several)
 #include "common.cuh"
 #include "paged_rows.cuh"
 
@@ -215,27 +215,55 @@ GB_EXPORT int gb_talking_attention_rows(const void* q, float* out, int dtype, co
 }
 
 // ----------------------------------------------------------------------------------------------
-// Single decoded tokens: one block of 8 warps per (row, R query heads of one key/value group). The warps take the row's
-// visible keys 32 at a time in turn (warp w the chunks w, w + 8, ...): a lane reads "its" key once and dots it with the R
-// queries; then the wide value rows of the 32 keys pass one after the other, a lane per channel, each value multiplied into
-// the R heads' sums. Every warp keeps a running maximum and a denominator per head of its own; at the end the warps meet in
-// shared memory (fixed order), where the unit of the denominator joins. The order of a row's sums depends on its position
-// and the window alone. R * NC <= 32 (NC = 32-channel pieces of the wide value row).
+// Single decoded tokens: one block of 8 warps per (row, R query heads of one key/value group, share of the row's keys). The
+// block's keys are taken 32 at a time by its warps in turn (warp w the chunks w, w + 8, ...): a lane reads "its" key once and
+// dots it with the R queries; then the wide value rows of the 32 keys pass KB at a time, a lane per channel: the KB rows'
+// loads are all asked for before the first is used (instructions issue in order: a loop that uses each row as it arrives
+// pays the trip to memory once per key), each value multiplied into the R heads' sums. Every warp keeps a running maximum
+// and a denominator per head of its own; the warps meet in shared memory (fixed order). With one share per row the unit of
+// the denominator joins there and the result is final; with several, every share leaves its sums, its maximum and its
+// denominator (part: [shares][n][H][wide], ml: [shares][n][H][2]) and talk_combine merges the shares on its way. The order of
+// a row's sums depends on its position, the window and the number of shares. R * NC <= 32 (NC = 32-channel pieces of the wide
+// value row).
 // ----------------------------------------------------------------------------------------------
 constexpr int TKD_WARPS = 8;
 
-template <typename T, int R, int NC>
+// NC consecutive bfloat16 channels of a value row as 32-bit words, in the widest pieces their alignment allows
+template <int NC>
+__device__ __forceinline__ void tkd_load_words(const __nv_bfloat16* __restrict__ p, unsigned (&w)[NC / 2]) {
+    if constexpr (NC % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < NC / 8; ++i) {
+            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (NC % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NC / 4; ++i) {
+            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NC / 2; ++i) w[i] = reinterpret_cast<const unsigned*>(p)[i];
+    }
+}
+
+// VEC (bfloat16, wide == 32 * NC, V a multiple of NC): a lane owns the NC consecutive channels lane * NC .. of the wide value
+// row and reads them with one to three loads per key; otherwise lane l owns the channels l, l + 32, ... and reads them one by one.
+template <typename T, int R, int NC, bool VEC>
 __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kernel(
-    const T* __restrict__ q, float* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+    const T* __restrict__ q, float* __restrict__ out, float* __restrict__ ml, const T* __restrict__ kcache, const T* __restrict__ vcache,
     const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
     int n, int H, int G, int D, int V, int VG, int page_size, long long num_pages, float scale, float cap, float unit, int window,
-    int* __restrict__ status) {
+    int shares, int* __restrict__ status) {
+    constexpr int KB = (NC > 8 && !VEC) ? 4 : 8;       // value rows in flight together
     __shared__ float qs[R * SA_MAX_DIM];
     __shared__ float part[TKD_WARPS][R][NC * 32 + 2];
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x, head0 = blockIdx.y * R;
+    const int row = blockIdx.x, head0 = blockIdx.y * R, share = blockIdx.z;
     if (row >= n) return;
     const int g = head0 / (H / G);
     const int pos = positions[row];
@@ -249,6 +277,9 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     __syncthreads();
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    // this block's share of the visible keys: whole chunks of 32, the same count for every share but the last
+    const int chunks = (pos - first) / 32 + 1, per_share = (chunks + shares - 1) / shares;
+    const int c_lo = share * per_share, c_hi = min(chunks, c_lo + per_share);
     const int wide = VG * V;
     float m[R], l[R], acc[R][NC];
     int voff[NC];
@@ -261,12 +292,12 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     }
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
-        const int i = lane + 32 * j;
+        const int i = VEC ? lane * NC + j : lane + 32 * j;
         const int c = VG == 1 ? g : i / V;
-        voff[j] = i < wide ? c * page_size * V + i % V : -1;
+        voff[j] = i < wide ? c * page_size * V + i % V : 0;          // (lanes past the row read a channel they never store)
     }
-    for (int base = first + warp * 32; base <= pos; base += TKD_WARPS * 32) {
-        const int key = base + lane;
+    for (int chunk = c_lo + warp; chunk < c_hi; chunk += TKD_WARPS) {
+        const int base = first + chunk * 32, key = base + lane;
         float s[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) s[r] = -INFINITY;
@@ -293,39 +324,69 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
 #pragma unroll
             for (int j = 0; j < NC; ++j) acc[r][j] *= corr;
         }
-        const int count = min(32, pos - base + 1);
-        for (int t = 0; t < count; ++t) {
-            const long long vr = __shfl_sync(0xffffffffu, at, t);
-            float pt[R];
+        // a key that cannot be read has weight 0; its loads go to the first row of the pool instead
+        const long long safe = at >= 0 ? at : 0;
+#pragma unroll 1
+        for (int t0 = 0; t0 < 32; t0 += KB) {
+            if (base + t0 > pos) break;
+            if constexpr (VEC) {
+                unsigned raw[KB][NC / 2];
 #pragma unroll
-            for (int r = 0; r < R; ++r) pt[r] = __shfl_sync(0xffffffffu, p[r], t);
-            if (vr < 0) continue;
-            const T* vp = vcache + vr * V;
-            float val[NC];
+                for (int u = 0; u < KB; ++u)
+                    tkd_load_words<NC>(reinterpret_cast<const __nv_bfloat16*>(vcache) + __shfl_sync(0xffffffffu, safe, t0 + u) * V + voff[0],
+                                       raw[u]);
 #pragma unroll
-            for (int j = 0; j < NC; ++j) val[j] = voff[j] >= 0 ? gb_to_float(vp[voff[j]]) : 0.f;
+                for (int u = 0; u < KB; ++u) {
+                    float pt[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r)
+                    for (int r = 0; r < R; ++r) pt[r] = __shfl_sync(0xffffffffu, p[r], t0 + u);
 #pragma unroll
-                for (int j = 0; j < NC; ++j) acc[r][j] = fmaf(pt[r], val[j], acc[r][j]);
+                    for (int j2 = 0; j2 < NC / 2; ++j2) {
+                        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u][j2]));
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            acc[r][2 * j2] = fmaf(pt[r], v.x, acc[r][2 * j2]);
+                            acc[r][2 * j2 + 1] = fmaf(pt[r], v.y, acc[r][2 * j2 + 1]);
+                        }
+                    }
+                }
+            } else {
+                float val[KB][NC];
+#pragma unroll
+                for (int u = 0; u < KB; ++u) {
+                    const T* vp = vcache + __shfl_sync(0xffffffffu, safe, t0 + u) * V;
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) val[u][j] = gb_to_float(vp[voff[j]]);
+                }
+#pragma unroll
+                for (int u = 0; u < KB; ++u) {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float pt = __shfl_sync(0xffffffffu, p[r], t0 + u);
+#pragma unroll
+                        for (int j = 0; j < NC; ++j) acc[r][j] = fmaf(pt, val[u][j], acc[r][j]);
+                    }
+                }
+            }
         }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
 #pragma unroll
-        for (int j = 0; j < NC; ++j) part[warp][r][lane + 32 * j] = acc[r][j];
+        for (int j = 0; j < NC; ++j) part[warp][r][VEC ? lane * NC + j : lane + 32 * j] = acc[r][j];
         if (lane == 0) {
             part[warp][r][NC * 32] = m[r];
             part[warp][r][NC * 32 + 1] = l[r];
         }
     }
     __syncthreads();
+    const bool final_ = shares == 1;
     for (int idx = threadIdx.x; idx < R * wide; idx += TKD_WARPS * 32) {
         const int r = idx / wide, i = idx % wide;
-        float top = unit > 0.f ? 0.f : -INFINITY;
+        float top = (final_ && unit > 0.f) ? 0.f : -INFINITY;
 #pragma unroll
         for (int w = 0; w < TKD_WARPS; ++w) top = fmaxf(top, part[w][r][NC * 32]);
-        float den = unit > 0.f ? unit * expf(-top) : 0.f, sum = 0.f;
+        float den = (final_ && unit > 0.f) ? unit * expf(-top) : 0.f, sum = 0.f;
         if (top > -INFINITY) {
 #pragma unroll
             for (int w = 0; w < TKD_WARPS; ++w) {
@@ -335,7 +396,16 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
                 sum = fmaf(part[w][r][i], f, sum);
             }
         }
-        out[((size_t)row * H + head0 + r) * wide + i] = den > 0.f ? sum / den : 0.f;
+        const size_t at = ((size_t)share * n + row) * H + head0 + r;
+        if (final_) {
+            out[at * wide + i] = den > 0.f ? sum / den : 0.f;
+        } else {
+            out[at * wide + i] = sum;
+            if (i == 0) {
+                ml[at * 2] = top;
+                ml[at * 2 + 1] = den;
+            }
+        }
     }
 }
 
@@ -351,19 +421,35 @@ GB_EXPORT int gb_talking_attention_decode_plan(int H, int G, int V, int VG) {
     return 0;
 }
 
-GB_EXPORT int gb_talking_attention_decode(const void* q, float* out, int dtype, const void* kcache, const void* vcache,
+// shares > 1: out is [shares][n][H][wide] and ml [shares][n][H][2], for talk_combine to merge; shares == 1: out is final
+GB_EXPORT int gb_talking_attention_decode(const void* q, float* out, float* ml, int dtype, const void* kcache, const void* vcache,
                                           const int* block_tables, int max_pages, const int* row_seq, const int* positions, int n, int H,
                                           int G, int D, int V, int VG, int page_size, long long num_pages, float scale, float cap,
-                                          float unit, int window, int* status, cudaStream_t stream) {
+                                          float unit, int window, int shares, int* status, cudaStream_t stream) {
     TK_COMMON_CHECKS("gb_talking_attention_decode")
     const int plan = gb_talking_attention_decode_plan(H, G, V, VG);
     GB_REQUIRE(plan > 0, "gb_talking_attention_decode: %d value heads of %d channels are not built", VG, V);
+    GB_REQUIRE(shares >= 1 && shares <= 64 && (shares == 1 || ml != nullptr), "gb_talking_attention_decode: %d shares", shares);
     if (n == 0) return 0;
     const int R = plan / 100, nc = plan % 100;
-    const dim3 grid(n, H / R);
-#define TKD_LAUNCH(T, RR, N)                                                                                                               gb_launch(GB_PDL_ATTENTION, talking_attention_decode_kernel<T, RR, N>, grid, dim3(TKD_WARPS * 32), 0, stream, (const T*)q, out,                   (const T*)kcache, (const T*)vcache, block_tables, max_pages, row_seq, positions, n, H, G, D, V, VG, page_size, num_pages,               scale, cap, unit, window, status)
-#define TKD_CASE(T, RR, N) if (R == RR && nc == N) { TKD_LAUNCH(T, RR, N); launched = true; }
-#define TKD_ALL(T)                                                                                                                          TKD_CASE(T, 1, 1) TKD_CASE(T, 1, 2) TKD_CASE(T, 1, 4) TKD_CASE(T, 1, 8) TKD_CASE(T, 1, 12) TKD_CASE(T, 1, 16)                           TKD_CASE(T, 2, 1) TKD_CASE(T, 2, 2) TKD_CASE(T, 2, 4) TKD_CASE(T, 2, 8) TKD_CASE(T, 2, 12) TKD_CASE(T, 2, 16)                           TKD_CASE(T, 4, 1) TKD_CASE(T, 4, 2) TKD_CASE(T, 4, 4) TKD_CASE(T, 4, 8)                                                                TKD_CASE(T, 8, 1) TKD_CASE(T, 8, 2) TKD_CASE(T, 8, 4)
+    const dim3 grid(n, H / R, shares);
+    // (the vector form: bfloat16, a wide row of exactly 32 * nc channels, a lane's nc channels inside one value head)
+    const bool vec = dtype == GB_BF16 && VG * V == 32 * nc && nc % 2 == 0 && V % nc == 0;
+#define TKD_LAUNCH(T, RR, N, VV)                                                                                                        \
+    gb_launch(GB_PDL_ATTENTION, talking_attention_decode_kernel<T, RR, N, VV>, grid, dim3(TKD_WARPS * 32), 0, stream, (const T*)q, out, \
+              ml, (const T*)kcache, (const T*)vcache, block_tables, max_pages, row_seq, positions, n, H, G, D, V, VG, page_size,        \
+              num_pages, scale, cap, unit, window, shares, status)
+#define TKD_CASE(T, RR, N)                                                                                                             \
+    if (R == RR && nc == N) {                                                                                                          \
+        if (sizeof(T) == 2 && N % 2 == 0 && vec) TKD_LAUNCH(T, RR, (N % 2 == 0 ? N : 2), (sizeof(T) == 2));                            \
+        else TKD_LAUNCH(T, RR, N, false);                                                                                              \
+        launched = true;                                                                                                               \
+    }
+#define TKD_ALL(T)                                                                                                                      \
+    TKD_CASE(T, 1, 1) TKD_CASE(T, 1, 2) TKD_CASE(T, 1, 4) TKD_CASE(T, 1, 8) TKD_CASE(T, 1, 12) TKD_CASE(T, 1, 16)                       \
+    TKD_CASE(T, 2, 1) TKD_CASE(T, 2, 2) TKD_CASE(T, 2, 4) TKD_CASE(T, 2, 8) TKD_CASE(T, 2, 12) TKD_CASE(T, 2, 16)                       \
+    TKD_CASE(T, 4, 1) TKD_CASE(T, 4, 2) TKD_CASE(T, 4, 4) TKD_CASE(T, 4, 8)                                                            \
+    TKD_CASE(T, 8, 1) TKD_CASE(T, 8, 2) TKD_CASE(T, 8, 4)
     bool launched = false;
     if (dtype == GB_F32) { TKD_ALL(float) }
     else if (dtype == GB_BF16) { TKD_ALL(__nv_bfloat16) }
@@ -624,42 +710,98 @@ GB_EXPORT int gb_talking_attention_tiles(const void* q, float* out, const void* 
 
 // ----------------------------------------------------------------------------------------------
 // The mix: att[row, h, :] = sum_g talk[h, g] * O[row, g, c(h), :] (talk == nullptr: O[row, h, c(h) or 0, :] as it is).
-// One thread per (row, h, channel).
+// shares > 1: O arrives in shares of the keys (o: [shares][n][H][wide] unnormalised sums, ml: [shares][n][H][2] each share's
+// maximum and denominator); the weights that merge them (and the unit of the denominator) are formed per (row, head) first.
+// One block per (row, key/value head c): it brings every head's result over c's values into shared memory once (merging the
+// shares on the way) and forms the outputs of the query heads whose key/value head is c.
 // ----------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) talk_combine_kernel(const float* __restrict__ o, const float* __restrict__ talk, T* __restrict__ att,
-                                                           const int* __restrict__ positions, int n, int H, int G, int V, int VG) {
+__global__ void __launch_bounds__(256) talk_combine_kernel(const float* __restrict__ o, const float* __restrict__ ml,
+                                                           const float* __restrict__ talk, T* __restrict__ att,
+                                                           const int* __restrict__ positions, int n, int H, int G, int V, int VG, int shares,
+                                                           float unit) {
+    extern __shared__ float tkc_smem[];
+    float* rows = tkc_smem;                  // [H][V]: head g's merged result over this block's value head
+    float* factor = rows + (size_t)H * V;    // [H][shares]: a share's weight in head g's merged softmax
     gb_pdl_launch_dependents();
     gb_pdl_wait();
-    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-    if (i >= (long long)n * H * V) return;
-    const int ch = (int)(i % V), h = (int)((i / V) % H), row = (int)(i / ((long long)V * H));
-    if (positions[row] < 0) return;
-    const int c = VG == 1 ? 0 : h / (H / G);
-    const float* src = o + (size_t)row * H * VG * V + (size_t)c * V + ch;
-    float acc;
-    if (talk == nullptr) {
-        acc = src[(size_t)h * VG * V];
-    } else {
-        acc = 0.f;
-        for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], src[(size_t)g * VG * V], acc);
+    const int row = blockIdx.x, c = blockIdx.y;
+    if (row >= n || positions[row] < 0) return;
+    const int wide = VG * V, per = H / G;
+    // without a mix only the heads of this group are read, each over its own values
+    const int g_lo = talk ? 0 : c * per, g_hi = talk ? H : (c + 1) * per;
+    const size_t col0 = VG == 1 ? 0 : (size_t)c * V;
+    if (shares > 1) {
+        for (int g = g_lo + threadIdx.x; g < g_hi; g += 256) {
+            float top = unit > 0.f ? 0.f : -INFINITY;
+            for (int z = 0; z < shares; ++z) top = fmaxf(top, ml[(((size_t)z * n + row) * H + g) * 2]);
+            float den = unit > 0.f ? unit * expf(-top) : 0.f;
+            for (int z = 0; z < shares; ++z) {
+                const float mz = ml[(((size_t)z * n + row) * H + g) * 2];
+                const float f = mz == -INFINITY ? 0.f : expf(mz - top);
+                den = fmaf(ml[(((size_t)z * n + row) * H + g) * 2 + 1], f, den);
+                factor[g * shares + z] = f;
+            }
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+            for (int z = 0; z < shares; ++z) factor[g * shares + z] *= inv;
+        }
+        __syncthreads();
     }
-    att[i] = gb_from_float<T>(acc);
+    for (int idx = g_lo * V + threadIdx.x; idx < g_hi * V; idx += 256) {
+        const int g = idx / V, ch = idx % V;
+        float v;
+        if (shares > 1) {
+            float a0 = 0.f, a1 = 0.f;
+            int z = 0;
+            for (; z + 2 <= shares; z += 2) {
+                a0 = fmaf(factor[g * shares + z], o[(((size_t)z * n + row) * H + g) * wide + col0 + ch], a0);
+                a1 = fmaf(factor[g * shares + z + 1], o[(((size_t)(z + 1) * n + row) * H + g) * wide + col0 + ch], a1);
+            }
+            if (z < shares) a0 = fmaf(factor[g * shares + z], o[(((size_t)z * n + row) * H + g) * wide + col0 + ch], a0);
+            v = a0 + a1;
+        } else {
+            v = o[((size_t)row * H + g) * wide + col0 + ch];
+        }
+        rows[idx] = v;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < per * V; idx += 256) {
+        const int h = c * per + idx / V, ch = idx % V;
+        float acc;
+        if (talk) {
+            float a0 = 0.f, a1 = 0.f;
+            int g = 0;
+            for (; g + 2 <= H; g += 2) {
+                a0 = fmaf(talk[h * H + g], rows[g * V + ch], a0);
+                a1 = fmaf(talk[h * H + g + 1], rows[(g + 1) * V + ch], a1);
+            }
+            if (g < H) a0 = fmaf(talk[h * H + g], rows[g * V + ch], a0);
+            acc = a0 + a1;
+        } else {
+            acc = rows[h * V + ch];
+        }
+        att[((size_t)row * H + h) * V + ch] = gb_from_float<T>(acc);
+    }
 }
 
-GB_EXPORT int gb_talk_combine(const float* o, const float* talk, void* att, int dtype, const int* positions, int n, int H, int G, int V,
-                              int VG, cudaStream_t stream) {
+template <typename T>
+static int tkc_launch(const float* o, const float* ml, const float* talk, void* att, const int* positions, int n, int H, int G, int V,
+                      int VG, int shares, float unit, cudaStream_t stream) {
+    const size_t smem = ((size_t)H * V + (size_t)H * shares) * sizeof(float);
+    GB_REQUIRE(smem <= 200 * 1024, "gb_talk_combine: %d heads of %d channels in %d shares do not fit a block's shared memory", H, V, shares);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(talk_combine_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gb_launch(GB_PDL_ELEMENTWISE, talk_combine_kernel<T>, dim3(n, G), dim3(256), smem, stream, o, ml, talk, (T*)att, positions, n, H, G, V,
+              VG, shares, unit);
+    return gb_check_launch("gb_talk_combine");
+}
+
+GB_EXPORT int gb_talk_combine(const float* o, const float* ml, const float* talk, void* att, int dtype, const int* positions, int n, int H,
+                              int G, int V, int VG, int shares, float unit, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && H > 0 && G > 0 && H % G == 0 && V > 0 && (VG == G || VG == 1), "gb_talk_combine: bad sizes");
     GB_REQUIRE(talk == nullptr || VG == G, "gb_talk_combine: mixing the heads needs every head's values");
+    GB_REQUIRE(shares >= 1 && (shares == 1 || ml != nullptr), "gb_talk_combine: %d shares of %d heads", shares, H);
     if (n == 0) return 0;
-    const int blocks = gb_ceil_div((long long)n * H * V, 256);
-    if (dtype == GB_F32)
-        gb_launch(GB_PDL_ELEMENTWISE, talk_combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, talk, (float*)att, positions, n, H, G,
-                  V, VG);
-    else if (dtype == GB_BF16)
-        gb_launch(GB_PDL_ELEMENTWISE, talk_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, o, talk, (__nv_bfloat16*)att,
-                  positions, n, H, G, V, VG);
-    else
-        GB_REQUIRE(false, "gb_talk_combine: unsupported dtype %d", dtype);
-    return gb_check_launch("gb_talk_combine");
+    if (dtype == GB_F32) return tkc_launch<float>(o, ml, talk, att, positions, n, H, G, V, VG, shares, unit, stream);
+    if (dtype == GB_BF16) return tkc_launch<__nv_bfloat16>(o, ml, talk, att, positions, n, H, G, V, VG, shares, unit, stream);
+    GB_REQUIRE(false, "gb_talk_combine: unsupported dtype %d", dtype);
 }

@@ -19,7 +19,9 @@ F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 #: the gate functions that the products' gated epilogues know (act = f(gate) * up)
-GATED_EPILOGUES = ("silu",)
+GATED_EPILOGUES = ("silu", "gelu_tanh")
+#: how the unit epilogues are told to form gelu_tanh(gate) * up instead of the clamped unit: (limit, slope)
+GELU_UNIT = (3.0e38, -1.0)
 
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot or page id outside the pool",
                4: "a position outside the rotary table or beyond a block table", 8: "a bounded wait inside a kernel gave up"}
@@ -104,11 +106,11 @@ _SIGNATURES = {
     "gb_scaled_sum": [_P, _P, _F, _F, _P, _LL, _I, _P],
     "gb_bias_rope_write": [_P, _LL, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _LL, _I, _P, _P],
     "gb_talking_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
-    "gb_talking_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
+    "gb_talking_attention_decode": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _I, _P, _P],
     "gb_talking_attention_decode_plan": [_I, _I, _I, _I],
     "gb_talking_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _F, _F, _I, _P, _P],
     "gb_talking_attention_tiles_columns": [_I, _I, _I],
-    "gb_talk_combine": [_P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "gb_talk_combine": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P],
     "gb_channel_delta_decode_supported": [_I, _I],
@@ -1164,7 +1166,7 @@ def channel_delta(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bia
           seq_start_pos.shape[0], heads, kv_heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status), dc, 0, _stream())
 
 
-CD_SILU_INPUTS, CD_PLAIN, CD_GATE_SILU = 1, 2, 4
+CD_SILU_INPUTS, CD_PLAIN, CD_GATE_SILU, CD_NO_NORM = 1, 2, 4, 8
 
 
 def decay_linear_attention(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,
@@ -1183,6 +1185,23 @@ def decay_linear_attention(qkv: torch.Tensor, decay: torch.Tensor, state: torch.
     _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), 0, 0, 0, 0, 0, _ptr(decay), _ptr(state), state.stride(0), _ptr(out),
           _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, heads, dk, dv, state.shape[0],
           1 if write_state else 0, _ptr(status), 1, CD_PLAIN | (CD_SILU_INPUTS if silu_inputs else 0), _stream())
+
+
+def decay_linear_attention_decode(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,
+                                  seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int, dk: int, dv: int, write_state: bool,
+                                  status: torch.Tensor, silu_inputs: bool = True) -> None:
+    """``decay_linear_attention`` for a step in which every request brings one row, on the delta rule's decoding form (S read and
+    written once, in whole rows); key and value size up to 128. out float32 [n, heads * dv]: the read-out as it is."""
+    _cuda(qkv, decay, state, out, seq_first_row, seq_start_pos, seq_slots, status)
+    n = qkv.shape[0]
+    for t in (qkv, decay, state, out):
+        assert t.dtype == torch.float32
+    assert qkv.shape[1] == 2 * heads * dk + heads * dv and qkv.stride(1) == 1 and out.shape == (n, heads * dv) and out.is_contiguous()
+    assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and decay.numel() == heads
+    _call("gb_channel_delta_decode", _ptr(qkv), qkv.stride(0), 0, 0, 0, 0, 0, _ptr(decay), _ptr(state), state.stride(0), 0, 0, 0, 0.0,
+          _ptr(out), F32, _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, heads, dk, dv,
+          state.shape[0], 1 if write_state else 0, _ptr(status), 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1,
+          CD_PLAIN | CD_NO_NORM | (CD_SILU_INPUTS if silu_inputs else 0), _stream())
 
 
 def residual_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torch.Tensor, state_off: int, row_seq: torch.Tensor,
@@ -1659,20 +1678,31 @@ def talking_attention_decode_supported(dtype: torch.dtype, heads: int, kv_heads:
     return dtype in _DT and bool(lib().gb_talking_attention_decode_plan(heads, kv_heads, vdim, value_heads))
 
 
+def talking_decode_shares(n: int, heads: int, kv_heads: int, vdim: int, value_heads: int, reach: int) -> int:
+    """Into how many shares the decoding kernel cuts a row's keys: enough blocks for two per multiprocessor, no share shorter
+    than 256 keys, at most 16."""
+    plan = lib().gb_talking_attention_decode_plan(heads, kv_heads, vdim, value_heads)
+    blocks = max(1, n * (heads // max(plan // 100, 1)))
+    return int(max(1, min(16, -(-296 // blocks), max(1, reach // 256), 4096 // heads)))
+
+
 def talking_attention_decode(q: torch.Tensor, wide: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                              row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
                              value_heads: int, page_size: int, scale: float, softcap: Optional[float], unit_sink: bool,
-                             window: Optional[int], status: torch.Tensor) -> None:
+                             window: Optional[int], status: torch.Tensor, shares: int = 1, ml: Optional[torch.Tensor] = None) -> None:
     """``talking_attention_rows`` for steps of single decoded tokens: a block of eight warps per (row, up to eight heads of a
-    key/value group) that take the row's keys in turn and merge in shared memory; a key row is read once for the block's heads."""
-    _cuda(q, wide, kcache, vcache, block_tables, row_seq, positions, status)
+    key/value group, share of the keys) that take the keys in turn and merge in shared memory; a key row is read once for the
+    block's heads. With ``shares`` > 1 ``wide`` is float32 [shares * n, heads * value_heads * vdim] (the shares' unnormalised
+    sums, share by share) and ``ml`` float32 [shares * n, heads * 2] their maxima and denominators: ``talk_combine`` merges them."""
+    _cuda(q, wide, kcache, vcache, block_tables, row_seq, positions, status, ml)
     n = q.shape[0]
     assert q.shape == (n, heads * dim) and q.is_contiguous() and q.dtype == kcache.dtype == vcache.dtype
-    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert wide.dtype == torch.float32 and wide.numel() == shares * n * heads * value_heads * vdim and wide.is_contiguous()
+    assert shares == 1 or (ml is not None and ml.dtype == torch.float32 and ml.numel() == shares * n * heads * 2 and ml.is_contiguous())
     assert block_tables.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and n <= 2 ** 31 - 1
-    _call("gb_talking_attention_decode", _ptr(q), _ptr(wide), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
-          _ptr(row_seq), _ptr(positions), n, heads, kv_heads, dim, vdim, value_heads, page_size, kcache.shape[0], float(scale),
-          float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), _ptr(status), _stream())
+    _call("gb_talking_attention_decode", _ptr(q), _ptr(wide), _ptr(ml), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+          block_tables.shape[1], _ptr(row_seq), _ptr(positions), n, heads, kv_heads, dim, vdim, value_heads, page_size, kcache.shape[0],
+          float(scale), float(softcap or 0.0), 1.0 if unit_sink else 0.0, int(window or 0), int(shares), _ptr(status), _stream())
 
 
 def talking_attention_tiles_supported(dtype: torch.dtype, dim: int, vdim: int, value_heads: int) -> bool:
@@ -1697,12 +1727,15 @@ def talking_attention_tiles(q: torch.Tensor, wide: torch.Tensor, kcache: torch.T
 
 
 def talk_combine(wide: torch.Tensor, talk: Optional[torch.Tensor], att: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int,
-                 vdim: int, value_heads: int) -> None:
+                 vdim: int, value_heads: int, shares: int = 1, ml: Optional[torch.Tensor] = None, unit_sink: bool = True) -> None:
     """att[row, h, :] = sum_g talk[h, g] * wide[row, g, c(h), :] with c(h) the key/value head of h (``talk`` None: head h's own
-    result as it is); talk float32 [heads, heads]."""
-    _cuda(wide, talk, att, positions)
+    result as it is); talk float32 [heads, heads]. With ``shares`` > 1 ``wide`` and ``ml`` are what the decoding kernel left
+    share by share, and the shares are merged (with the unit of the denominator, if ``unit_sink``) on the way."""
+    _cuda(wide, talk, att, positions, ml)
     n = att.shape[0]
-    assert wide.dtype == torch.float32 and wide.shape == (n, heads * value_heads * vdim) and wide.is_contiguous()
+    assert wide.dtype == torch.float32 and wide.numel() == shares * n * heads * value_heads * vdim and wide.is_contiguous()
+    assert shares == 1 or (ml is not None and ml.dtype == torch.float32 and ml.numel() == shares * n * heads * 2)
     assert att.shape == (n, heads * vdim) and att.is_contiguous()
     assert talk is None or (talk.dtype == torch.float32 and talk.shape == (heads, heads) and talk.is_contiguous())
-    _call("gb_talk_combine", _ptr(wide), _ptr(talk), _ptr(att), _dt(att), _ptr(positions), n, heads, kv_heads, vdim, value_heads, _stream())
+    _call("gb_talk_combine", _ptr(wide), _ptr(ml), _ptr(talk), _ptr(att), _dt(att), _ptr(positions), n, heads, kv_heads, vdim, value_heads,
+          int(shares), 1.0 if unit_sink else 0.0, _stream())

@@ -27,6 +27,9 @@ over operands that rotate through more memory than L2 holds.
                                                                          a product's epilogue beside SwiGLU in the same product; the
                                                                          routed clamped experts beside a dense product of as many
                                                                          multiply-adds; the router
+    python -m glassbox_b200.microbench babotar                           Babotar's kernels, each beside its like kernel: talking-heads
+                                                                         attention, lightning attention and the delta rule with one decay
+                                                                         per head, the input convolution, the GELU unit in the products
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -560,6 +563,140 @@ def bench_tagenex() -> None:
     kernels.check_status(status)
 
 
+def bench_babotar() -> None:
+    """Each kernel of the Babotar path beside the like kernel of the closest path, at the sizes of the width-1024 and
+    width-2048 models that ``bench.py --workload babotar`` runs."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ps, hd, t_len, ctx = 16, 64, 2048, 4096
+    for H, G in ((16, 4), (32, 8)):
+        per = t_len // ps
+        kc = torch.randn(per + 2, G, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        tables = torch.arange(per, dtype=torch.int32, device=DEV).view(1, per).contiguous()
+        first = torch.tensor([0, t_len], dtype=torch.int32, device=DEV)
+        start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        pos = torch.arange(t_len, dtype=torch.int32, device=DEV)
+        q = torch.randn(t_len, H * hd, device=DEV).bfloat16()
+        o = torch.empty_like(q)
+        wide = torch.empty(t_len, H * G * hd, device=DEV)
+        talk = torch.eye(H, device=DEV) + 0.1 * torch.randn(H, H, device=DEV)
+        own = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, value_heads=G, page_size=ps, scale=hd ** -0.5, softcap=50.0, unit_sink=True,
+                   window=None, status=status)
+        seen = t_len * (t_len + 1) // 2
+        fl_own, fl_like = 2.0 * seen * H * (hd + G * hd), 2.0 * seen * H * (hd + hd)
+        t = graph_time(lambda: kernels.talking_attention_tiles(q, wide, kc, vc, tables, first, start, t_len, **own), reps=4)
+        print(f"talking_attention prompt (mma.sync tiles, every head over {G} value heads) heads {H}/{G} x {hd}, {t_len} tokens: {t:7.1f} us "
+              f"{fl_own / t / 1e6:6.1f} TFLOP/s", flush=True)
+        t = graph_time(lambda: kernels.talk_combine(wide, talk, o, pos, H, G, hd, G), reps=4)
+        print(f"   mix of the heads, {t_len} rows: {t:7.1f} us {(wide.numel() * 4 + o.numel() * 2) / t / 1e3:6.0f} GB/s", flush=True)
+        for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
+            t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, H, G, hd, ps, hd ** -0.5, None, status), reps=4)
+            print(f"   grouped-query prompt ({name}) the same heads: {t:7.1f} us {fl_like / t / 1e6:6.1f} TFLOP/s", flush=True)
+        cols = (H + 2 * G) * hd
+        from .parts.rope import rotary_table
+        rope = rotary_table(10000.0, hd, 8192).to(DEV)
+        for n in (t_len, 8):
+            proj, bias = torch.randn(n, cols, device=DEV), torch.randn(cols, device=DEV)
+            qo = torch.empty(n, H * hd, device=DEV).bfloat16()
+            p = pos[:n]
+            t = graph_time(lambda: kernels.bias_rope_write(proj, bias, rope, p, p, qo, kc, vc, H, G, hd, hd, hd, ps, True, status))
+            print(f"bias + rotation + cache write heads {H}/{G}, {n:4d} rows: {t:6.1f} us {n * cols * 6 / t / 1e3:6.0f} GB/s", flush=True)
+            qkv = torch.randn(n, cols, device=DEV).bfloat16()
+            t = graph_time(lambda: kernels.rope_kv_write(qkv, rope, p, p, kc, vc, H, G, hd, hd, ps, True, status))
+            print(f"   rotation + cache write, {n:4d} rows: {t:6.1f} us {n * cols * 4 / t / 1e3:6.0f} GB/s", flush=True)
+        for m in (1, 8, 64):
+            per = ctx // ps
+            kd = torch.randn(m * per + 4, G, ps, hd, device=DEV).bfloat16()
+            vd = torch.randn_like(kd)
+            tb = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+            row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+            pd = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+            qd = torch.randn(m, H * hd, device=DEV).bfloat16()
+            od = torch.empty_like(qd)
+            wd = torch.empty(m, H * G * hd, device=DEV)
+            nbytes = m * ctx * G * hd * 2 * 2
+            shares = kernels.talking_decode_shares(m, H, G, hd, G, ctx)
+            wd = torch.empty(shares * m, H * G * hd, device=DEV)
+            mld = torch.empty(shares * m, H * 2, device=DEV)
+            t = graph_time(lambda: kernels.talking_attention_decode(qd, wd, kd, vd, tb, row_seq, pd, shares=shares, ml=mld, **own))
+            t2 = graph_time(lambda: kernels.talk_combine(wd, talk, od, pd, H, G, hd, G, shares=shares, ml=mld))
+            print(f"talking_attention decode heads {H}/{G} x {hd} batch {m:3d} context {ctx}, {shares:2d} shares: {t:7.1f} us "
+                  f"{nbytes / t / 1e3:6.0f} GB/s (the cache once); merge + mix of the heads {t2:6.1f} us", flush=True)
+            sp, block_keys, warps = kernels.decode_mma_plan(m, G, hd, ctx)
+            pa = torch.empty(m * H * warps * sp * hd, device=DEV)
+            pm = torch.empty(m * H * warps * sp * 2, device=DEV)
+            cn = torch.zeros(m * G, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(qd, od, kd, vd, tb, row_seq, pd, H, G, hd, ps, hd ** -0.5, None, sp, pa, pm,
+                                                                cn, status, block_keys, warps))
+            print(f"   grouped-query decode (split keys) the same: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    # the recurrences: lightning attention and the delta rule with one decay per head, key and value size 128
+    dk = dv = 128
+    for H in (8, 16):
+        for n, S in ((2048, 1), (1, 1), (8, 8), (64, 64)):
+            per = n // S
+            qkv = torch.randn(n, 2 * H * dk + H * dv, device=DEV)
+            decay = torch.full((H,), 0.97, device=DEV)
+            first = torch.arange(0, n + 1, per, dtype=torch.int32, device=DEV)
+            start = torch.zeros(S, dtype=torch.int32, device=DEV)
+            slots = torch.arange(S, dtype=torch.int32, device=DEV)
+            copies = max(1, int(2 * L2_BYTES / (S * H * dk * dv * 4)))
+            states = [torch.zeros(S, H * dk * dv, device=DEV) for _ in range(min(copies, 8))]
+            out = torch.empty(n, H * dv, device=DEV)
+            turn = [0]
+
+            def lightning():
+                turn[0] += 1
+                run = kernels.decay_linear_attention_decode if per == 1 else kernels.decay_linear_attention
+                run(qkv, decay, states[turn[0] % len(states)], out, first, start, slots, H, dk, dv, True, status)
+            t = graph_time(lightning, reps=3 if per > 1 else 12)
+            beta, a, gate = torch.randn(n, H, device=DEV), torch.randn(n, H, device=DEV), torch.randn(n, H * dv, device=DEV)
+            dt, al, w = torch.randn(H, device=DEV), torch.zeros(H, device=DEV), torch.ones(dv, device=DEV)
+            if per == 1:
+                att = torch.empty(n, H * dv, device=DEV).bfloat16()
+
+                def delta():
+                    turn[0] += 1
+                    kernels.channel_delta_decode(qkv, beta, a, dt, al, states[turn[0] % len(states)], gate, w, 1e-6, att, first, start,
+                                                 slots, H, H, dk, dv, True, status, decay_per_head=True, gate_silu=True)
+                t2 = graph_time(delta)
+                nbytes = 2.0 * S * H * dk * dv * 4
+                print(f"lightning single tokens heads {H} x {dk} x {dv}, {S:2d} requests: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s; "
+                      f"delta rule (one decay per head, decoding form): {t2:7.1f} us {nbytes / t2 / 1e3:6.0f} GB/s", flush=True)
+            else:
+                t2 = graph_time(lambda: kernels.channel_delta(qkv, beta, a, dt, al, states[0], out, first, start, slots, H, H, dk, dv, True,
+                                                              status, decay_per_head=True), reps=3)
+                print(f"lightning prompt heads {H} x {dk} x {dv}, {n} tokens: {t:7.1f} us = {t / n:5.3f} us per token; delta rule "
+                      f"(one decay per head): {t2:7.1f} us = {t2 / n:5.3f} us per token", flush=True)
+    # the convolution on the mixers' input and the gated GELU unit in the products' epilogues
+    for d, ff in ((1024, 4096), (2048, 8192)):
+        for n in (2048, 64, 8):
+            x = torch.randn(n, d, device=DEV).bfloat16()
+            y = torch.empty_like(x)
+            w = torch.randn(d, 4, device=DEV)
+            state = torch.zeros(1, 3 * d, device=DEV)
+            row_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+            pos = torch.arange(n, dtype=torch.int32, device=DEV)
+            first = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+            zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.residual_conv(x, w, y, state, 0, row_seq, pos, first, zero, zero, True, status))
+            print(f"input convolution (4 taps, two launches) {n:4d} rows x {d}: {t:6.1f} us {n * d * 4 / t / 1e3:6.0f} GB/s", flush=True)
+            ws = _rotating(2 * ff, d)
+            act = torch.empty(n, ff, device=DEV).bfloat16()
+            turn = [0]
+            for unit, args in (("gelu", kernels.GELU_UNIT), ("clamped", (7.0, 1.702))):
+                def fn():
+                    turn[0] += 1
+                    wm = ws[turn[0] % len(ws)]
+                    if n > kernels.STREAM_MAX_ROWS:
+                        kernels.gemm_tc_unit(x, wm, None, args[0], args[1], act, status)
+                    else:
+                        kernels.gemm_stream_unit(x, wm, None, args[0], args[1], act)
+                t = graph_time(fn)
+                print(f"gated unit ({unit}) in the product's epilogue {n:4d} rows, {d} -> 2 x {ff}: {t:7.1f} us "
+                      f"{2.0 * n * d * 2 * ff / t / 1e6:7.1f} TFLOP/s {2 * ff * d * 2 / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
 def bench_float32() -> None:
     """The kernels of the true 32-bit path at SmolLM2-135M shapes: FMA products for a 2,048-token prompt and for 8
     decoded rows, split-key decode attention and one-warp-per-row attention over a float32 cache."""
@@ -742,7 +879,7 @@ def bench_layer_gemms(rows) -> None:
     kernels.check_status(st)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule", "lonorax", "tagenex")
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule", "lonorax", "tagenex", "babotar")
 
 
 def main(argv) -> int:
@@ -780,6 +917,8 @@ def main(argv) -> int:
         bench_lonorax()
     elif argv[0] == "tagenex":
         bench_tagenex()
+    elif argv[0] == "babotar":
+        bench_babotar()
     else:
         bench_attention_prefill()
     return 0

@@ -97,6 +97,11 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor, unit: str =
     function; a unit for which the products have no epilogue is never fused."""
     if unit not in kernels.GATED_EPILOGUES:
         return False
+    if unit == "gelu_tanh":
+        # the unit epilogues of both products form it (from the float32 sums) when told so
+        if isinstance(a, DeferredNorm):
+            a = a.tensor()
+        return clamped_glu_linear(ctx, a, w_gate_up, None, *kernels.GELU_UNIT, act)
     inter = w_gate_up.shape[0] // 2
     x, norm, _, scale = _resolve(a, w_gate_up)
     if scale is not None:

@@ -60,8 +60,11 @@ class DecayLinearAttention(Mixer):
         proj = ctx.scratch("lin_proj", (n, ld), f32)[:, :self.in_cols]
         linear(ctx, h, self.params["w_in"], proj)
         o = ctx.scratch("lin_o", (n, self.v_cols), f32)
-        kernels.decay_linear_attention(proj[:, :self.gate_at], self._decay, cache.state, o, ctx.seq_first_row, ctx.seq_start_pos,
-                                       ctx.seq_slots, self.H, self.dk, self.dv, writes_cache, ctx.status, silu_inputs=True)
+        # single tokens: the form that reads and writes S once, in whole rows; portions: the walk over tokens
+        run = (kernels.decay_linear_attention_decode if ctx.decode_only and kernels.channel_delta_decode_supported(self.dk, self.dv)
+               else kernels.decay_linear_attention)
+        run(proj[:, :self.gate_at], self._decay, cache.state, o, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, self.H, self.dk,
+            self.dv, writes_cache, ctx.status, silu_inputs=True)
         att = ctx.scratch("att", (n, self.v_cols))
         # the norm runs over the concatenated heads: one "head" of heads * value_dim channels
         kernels.gated_head_norm(o, proj[:, self.gate_at:], self.params["out_norm"], att, 1, self.spec.norm_eps)

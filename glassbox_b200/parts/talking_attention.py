@@ -85,24 +85,30 @@ class TalkingAttention(Mixer):
         kernels.bias_rope_write(proj, p.get("b_in"), table, ctx.positions, cache.slots, q, cache.k, cache.v, self.H, self.G, self.D,
                                 self.V, self.rot, cache.page_size, writes_cache, ctx.status)
         value_heads = self.G if s.talk else 1
-        wide = ctx.scratch("tk_wide", (n, self.H * value_heads * self.V), torch.float32)
-        self.attend(ctx, q, wide, cache, value_heads)
-        att = ctx.scratch("att", (n, self.H * self.V))
-        kernels.talk_combine(wide, p.get("talk"), att, ctx.positions, self.H, self.G, self.V, value_heads)
-        linear(ctx, att, p["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
-
-    def attend(self, ctx, q, wide, cache, value_heads: int) -> None:
-        s = self.spec
+        cols = self.H * value_heads * self.V
+        how = pick_kernel(q.dtype, ctx.decode_only, self.H, self.G, self.D, self.V, value_heads)
         common = dict(heads=self.H, kv_heads=self.G, dim=self.D, vdim=self.V, value_heads=value_heads, page_size=cache.page_size,
                       scale=s.scale, softcap=s.softcap, unit_sink=s.unit_sink, window=s.window, status=ctx.status)
-        how = pick_kernel(q.dtype, ctx.decode_only, self.H, self.G, self.D, self.V, value_heads)
+        shares, ml = 1, None
         if how == "decode":
-            kernels.talking_attention_decode(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
-        elif how == "tiles":
-            kernels.talking_attention_tiles(q, wide, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,
-                                            ctx.max_rows_per_seq, **common)
+            # few rows: the keys of a row are cut into shares, so that the blocks fill the chip; the mix merges the shares
+            reach = min(ctx.max_context, s.window) if s.window else ctx.max_context
+            shares = kernels.talking_decode_shares(n, self.H, self.G, self.V, value_heads, reach)
+            wide = ctx.scratch("tk_wide_shares", (n, shares * cols), torch.float32, grow=True)
+            ml = ctx.scratch("tk_ml", (n, shares * self.H * 2), torch.float32, grow=True) if shares > 1 else None
+            kernels.talking_attention_decode(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, shares=shares, ml=ml,
+                                             **common)
         else:
-            kernels.talking_attention_rows(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
+            wide = ctx.scratch("tk_wide", (n, cols), torch.float32)
+            if how == "tiles":
+                kernels.talking_attention_tiles(q, wide, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,
+                                                ctx.max_rows_per_seq, **common)
+            else:
+                kernels.talking_attention_rows(q, wide, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions, **common)
+        att = ctx.scratch("att", (n, self.H * self.V))
+        kernels.talk_combine(wide, p.get("talk"), att, ctx.positions, self.H, self.G, self.V, value_heads, shares=shares, ml=ml,
+                             unit_sink=s.unit_sink)
+        linear(ctx, att, p["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
 
 register_part("mixer", "talking_attention", TalkingAttention, replace=True)

@@ -191,6 +191,33 @@ def test_gelu_gated_unit_and_weighted_sum():
     np.testing.assert_allclose(o.cpu().numpy(), 0.6 * a - 1.5 * b, atol=1e-6)
 
 
+@pytest.mark.parametrize("n, ff, d", [(1, 64, 128), (8, 48, 72), (64, 256, 128), (65, 64, 128), (300, 136, 64), (2048, 512, 256)])
+def test_gelu_gated_unit_in_a_products_epilogue(n, ff, d):
+    """The two products of a feed-forward's first half with gelu_tanh(gate) * up formed from their float32 sums, in the kernel
+    for few rows (the weights streamed once) and in the tile kernel."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(n + ff)
+    bf = lambda a: _f32(a).to(torch.bfloat16)
+    h, w = bf(rng.standard_normal((n, d))), bf(rng.standard_normal((2 * ff, d)) * 2.0 / np.sqrt(d))
+    z = h.float().cpu().numpy().astype(np.float64) @ w.float().cpu().numpy().astype(np.float64).T
+    want = plain.gelu_tanh(z[:, :ff]) * z[:, ff:]
+    limit, slope = kernels.GELU_UNIT
+    ran = 0
+    if kernels.gemm_stream_supported(h, w) and ff % 16 == 0:
+        act = torch.zeros((n, ff), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_stream_unit(h, w, None, limit, slope, act)
+        np.testing.assert_allclose(act.float().cpu().numpy(), want, atol=2e-2, rtol=1e-2)
+        ran += 1
+    act = torch.zeros((n, ff), dtype=torch.bfloat16, device=DEV)
+    if kernels.gemm_tc_supported(h, w, act):
+        status = _status()
+        kernels.gemm_tc_unit(h, w, None, limit, slope, act, status)
+        assert int(status.item()) == 0
+        np.testing.assert_allclose(act.float().cpu().numpy(), want, atol=2e-2, rtol=1e-2)
+        ran += 1
+    assert ran >= 1
+
+
 def _identity_rows(pieces):
     """{name: rows of an identity matrix} that pick the named parts of a stacked row apart."""
     eye, out, at = np.eye(sum(n for _, n in pieces)), {}, 0
@@ -216,17 +243,21 @@ def test_lightning_recurrence_norm_and_gate(H, D, V):
     slots = [2, 0, 3]
     state = torch.zeros((5, H * D * V + 5), device=DEV)
     state[[1, 4]] = 3.0
-    got, at, status = [np.zeros((n, H * V)) for n in lengths], [0] * len(lengths), _status()
+    got, at, status, used = [np.zeros((n, H * V)) for n in lengths], [0] * len(lengths), _status(), set()
     for step in _cuts(lengths, rng):
         n, row_seq, positions, first, start = _step_meta(step, at)
         proj = _f32(_gather(step, at, rows_in, cols))
         o = torch.zeros((n, H * V), device=DEV)
         att = torch.zeros((n, H * V), device=DEV)
         seq_slots = _i32([0 if e is None else slots[e[0]] for e in step])
-        kernels.decay_linear_attention(proj[:, :2 * H * D + H * V], _f32(decay), state, o, first, start, seq_slots, H, D, V, True, status)
+        single = all(e is None or e[1] == 1 for e in step)
+        run = kernels.decay_linear_attention_decode if single and kernels.channel_delta_decode_supported(D, V) else kernels.decay_linear_attention
+        used.add(run.__name__)
+        run(proj[:, :2 * H * D + H * V], _f32(decay), state, o, first, start, seq_slots, H, D, V, True, status)
         kernels.gated_head_norm(o, proj[:, 2 * H * D + H * V:], _f32(W["norm"]), att, 1, 1e-5)
         _scatter(step, at, att.cpu().numpy(), got)
     assert int(status.item()) == 0 and bool((state[[1, 4]] == 3.0).all())
+    assert ("decay_linear_attention_decode" in used) == (D <= 128 and V <= 128) and "decay_linear_attention" in used
     for r in range(len(lengths)):
         want = plain.lightning(rows_in[r], W, "", m, 1e-5)
         np.testing.assert_allclose(got[r], want, atol=3e-5 * max(1.0, np.abs(want).max()), rtol=1e-4, err_msg=f"request {r}")
@@ -309,7 +340,14 @@ def _attend(kernels, how, q, wide, cache, tables, row_seq, positions, first, sta
     if how == "fast":
         picked = ta.pick_kernel(q.dtype, single, common["heads"], common["kv_heads"], common["dim"], common["vdim"], common["value_heads"])
         if picked == "decode":
-            return kernels.talking_attention_decode(q, wide, cache.k, cache.v, tables, row_seq, positions, **common)
+            # another number of shares of the keys at every step; the mix then merges the shares
+            n, shares = q.shape[0], [1, 3, 2, 5, 16][int(positions.max().item()) % 5]
+            if shares == 1:
+                return kernels.talking_attention_decode(q, wide, cache.k, cache.v, tables, row_seq, positions, **common)
+            parts = torch.full((shares * n, wide.shape[1]), float("nan"), device=DEV)
+            ml = torch.full((shares * n, common["heads"] * 2), float("nan"), device=DEV)
+            kernels.talking_attention_decode(q, parts, cache.k, cache.v, tables, row_seq, positions, shares=shares, ml=ml, **common)
+            return parts, ml, shares
         if picked == "tiles":
             return kernels.talking_attention_tiles(q, wide, cache.k, cache.v, tables, first, start, longest, **common)
     kernels.talking_attention_rows(q, wide, cache.k, cache.v, tables, row_seq, positions, **common)
@@ -345,9 +383,12 @@ def _run_left_steps(kernels, how, steps, lengths, rows_in, m, W, cache, dtype, t
         tables = _i32([[-1] * cache.width if e is None else cache.row(e[0]) for e in step])
         wide = torch.full((n, H * VG * V), float("nan"), device=DEV)
         single = all(e is None or e[1] == 1 for e in step)
-        _attend(kernels, how, q, wide, cache, tables, row_seq, positions, first, start, max(e[1] for e in step if e), single, common)
+        shared = _attend(kernels, how, q, wide, cache, tables, row_seq, positions, first, start, max(e[1] for e in step if e), single, common)
         att = torch.zeros((n, H * V), dtype=dtype, device=DEV)
-        kernels.talk_combine(wide, _f32(W["talk"]) if talk else None, att, positions, H, G, V, VG)
+        if shared is not None:
+            kernels.talk_combine(shared[0], _f32(W["talk"]) if talk else None, att, positions, H, G, V, VG, shares=shared[2], ml=shared[1])
+        else:
+            kernels.talk_combine(wide, _f32(W["talk"]) if talk else None, att, positions, H, G, V, VG)
         _scatter(step, at, att.float().cpu().numpy(), got)
     assert int(status.item()) == 0
     return got
