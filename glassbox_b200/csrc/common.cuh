@@ -54,6 +54,12 @@ __device__ __forceinline__ float gb_gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// The same through the identity 0.5 (1 + tanh(y)) = 1 / (1 + exp(-2 y)) with the hardware's exponential and division (a
+// relative error near 1e-6): for epilogues that round the result to bfloat16.
+__device__ __forceinline__ float gb_gelu_tanh_fast(float z) {
+    return __fdividef(z, 1.0f + __expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -392,6 +392,177 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
 }
 
 // ----------------------------------------------------------------------------------------------
+// Linear attention with a FIXED decay per head over long portions, cut into pieces. With g constant the state after a piece
+// is g^L S_start + B, where B (the piece's own sum of g^(L-1-j) k_j v_j^T) does not depend on S_start, and a token's read-out
+// is its read-out from a zero state at the piece's start plus g^(i+1) q^T S_start (i its index in the piece). So the pieces of
+// a request walk side by side, each from zero (the kernel above, one "sequence" per piece, into a scratch state per piece),
+// a second kernel chains the pieces' states (an element of S per thread: S_start of every piece replaces its B, the request's
+// slot receives the last), and a third adds q^T S_start to the read-outs as a small float32 product per piece. The chain of
+// dependent updates is one piece long instead of one portion long. Float32 throughout; only the order of the sums differs
+// from the walk over the whole portion.
+// ----------------------------------------------------------------------------------------------
+// meta: piece_first_row [P + 1] | piece_start [P] (0, or -1 for an unused piece) | piece_slot [P] (= its index) | piece_seq [P] |
+//       seq_piece_lo [S] | seq_piece_hi [S] (a request's pieces; empty for a padding sequence)
+__global__ void lin_pieces_plan_kernel(const int* __restrict__ seq_first_row, const int* __restrict__ seq_start_pos, int S, int P,
+                                       int piece_len, int* __restrict__ meta) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int* first = meta, *start = meta + P + 1, *slot = start + P, *pseq = slot + P, *piece_lo = pseq + P, *piece_hi = piece_lo + S;
+    int p = 0, last_row = 0;
+    for (int s = 0; s < S; ++s) {
+        const int r0 = seq_first_row[s], r1 = seq_first_row[s + 1];
+        const int p_before = p;
+        if (r1 > r0) last_row = r1;
+        // the pieces tile the step's rows: a padding sequence's rows are one unused piece
+        const bool live = seq_start_pos[s] >= 0;
+        for (int r = r0; r < r1 && p < P; r += live ? piece_len : r1 - r0) {
+            first[p] = r;
+            start[p] = live ? 0 : -1;
+            slot[p] = p;
+            pseq[p] = s;
+            ++p;
+        }
+        piece_lo[s] = live ? p_before : p;       // (a padding sequence's piece belongs to no request)
+        piece_hi[s] = p;
+    }
+    for (int i = p; i < P; ++i) { first[i] = last_row; start[i] = -1; slot[i] = i; pseq[i] = 0; }
+    first[P] = last_row;
+}
+
+// the rows of piece p end where piece p + 1 begins
+__device__ __forceinline__ int lin_piece_end(const int* __restrict__ meta, int P, const int* __restrict__ seq_first_row, int p) {
+    return meta[p + 1];
+}
+
+__global__ void __launch_bounds__(256) lin_chain_kernel(const int* __restrict__ meta, int P, const int* __restrict__ seq_first_row,
+                                                        const int* __restrict__ seq_start_pos, const int* __restrict__ seq_slots,
+                                                        const float* __restrict__ decay, float* __restrict__ piece_state,
+                                                        float* __restrict__ state, long long state_stride, int S, int heads, int numbers,
+                                                        int num_slots, int write_state) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int e = blockIdx.z * 256 + threadIdx.x;           // an element of the head's S
+    if (seq >= S || e >= numbers || seq_start_pos[seq] < 0) return;
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= num_slots) return;
+    const int* first = meta, *piece_lo = meta + 4 * P + 1, *piece_hi = piece_lo + S;
+    float* mine = state + (size_t)slot * state_stride + (size_t)head * numbers + e;
+    float s = *mine;
+    const float g = decay[head];
+    // eight pieces at a time: their own sums and lengths are all asked for before the chain through them starts
+    for (int p0 = piece_lo[seq]; p0 < piece_hi[seq]; p0 += 8) {
+        float own[8], f[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int p = min(p0 + u, piece_hi[seq] - 1);
+            own[u] = piece_state[((size_t)p * heads + head) * numbers + e];
+            f[u] = powf(g, (float)(lin_piece_end(meta, P, seq_first_row, p) - first[p]));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (p0 + u >= piece_hi[seq]) break;
+            piece_state[((size_t)(p0 + u) * heads + head) * numbers + e] = s;      // the state this piece starts from
+            s = fmaf(f[u], s, own[u]);
+        }
+    }
+    if (write_state) *mine = s;
+}
+
+constexpr int LC_ROWS = 128, LC_COLS = 64, LC_K = 32;
+
+__global__ void __launch_bounds__(256) lin_carry_kernel(const float* __restrict__ qkv, long long ldq, const int* __restrict__ meta, int P,
+                                                        const int* __restrict__ seq_first_row, const float* __restrict__ decay,
+                                                        const float* __restrict__ piece_state, float* __restrict__ out, int heads, int dk,
+                                                        int dv, int piece_len, int silu_in) {
+    __shared__ float qs[LC_ROWS][LC_K + 1];
+    __shared__ float ss[LC_K][LC_COLS];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * LC_COLS;
+    const int* first = meta, *start = meta + P + 1;
+    if (start[p] < 0) return;
+    const int r0 = first[p], rows = lin_piece_end(meta, P, seq_first_row, p) - r0;
+    const float* S0 = piece_state + ((size_t)p * heads + head) * dk * dv;
+    const float g = decay[head];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // 16 x 16 threads: 4 columns x 8 rows each
+    for (int rb = 0; rb < rows; rb += LC_ROWS) {
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        for (int k0 = 0; k0 < dk; k0 += LC_K) {
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < LC_ROWS * LC_K; idx += 256) {
+                const int r = idx / LC_K, d = idx % LC_K;
+                float v = 0.f;
+                if (rb + r < rows && k0 + d < dk) {
+                    v = qkv[(size_t)(r0 + rb + r) * ldq + (size_t)head * dk + k0 + d];
+                    if (silu_in) v = cd_silu(v);
+                }
+                qs[r][d] = v;
+            }
+            for (int idx = threadIdx.x; idx < LC_K * LC_COLS; idx += 256) {
+                const int d = idx / LC_COLS, c = idx % LC_COLS;
+                ss[d][c] = (k0 + d < dk && c0 + c < dv) ? S0[(size_t)(k0 + d) * dv + c0 + c] : 0.f;
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int d = 0; d < LC_K; ++d) {
+                const float4 sv = *reinterpret_cast<const float4*>(&ss[d][tx * 4]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float qv = qs[ty * 8 + i][d];
+                    acc[i][0] = fmaf(qv, sv.x, acc[i][0]);
+                    acc[i][1] = fmaf(qv, sv.y, acc[i][1]);
+                    acc[i][2] = fmaf(qv, sv.z, acc[i][2]);
+                    acc[i][3] = fmaf(qv, sv.w, acc[i][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = rb + ty * 8 + i;
+            if (r >= rows) continue;
+            const float f = powf(g, (float)(r + 1));
+            float* dst = out + (size_t)(r0 + r) * heads * dv + (size_t)head * dv + c0 + tx * 4;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c0 + tx * 4 + c < dv) dst[c] = fmaf(f, acc[i][c], dst[c]);
+        }
+    }
+}
+
+// meta: int32 [4 * P + 2 * S + 1]; piece_state: float32 [P, heads * dk * dv]. P must be at least n / piece_len + S.
+GB_EXPORT int gb_decay_linear_pieces(const float* qkv, long long ldq, const float* decay, float* state, long long state_stride, float* out,
+                                     const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int n, int heads,
+                                     int dk, int dv, int num_slots, int write_state, int* status, int silu_in, int piece_len, int P,
+                                     int* meta, float* piece_state, cudaStream_t stream) {
+    GB_REQUIRE(S >= 0 && n >= 0 && heads > 0 && dk > 0 && dk <= 1024 && dv > 0 && piece_len >= 16, "gb_decay_linear_pieces: bad sizes");
+    GB_REQUIRE(P >= n / piece_len + S && meta && piece_state, "gb_decay_linear_pieces: %d pieces are too few for %d rows of %d requests",
+               P, n, S);
+    if (S == 0 || n == 0) return 0;
+    const size_t numbers = (size_t)dk * dv;
+    if (cudaMemsetAsync(piece_state, 0, (size_t)P * heads * numbers * sizeof(float), stream) != cudaSuccess)
+        GB_REQUIRE(false, "gb_decay_linear_pieces: clearing the pieces' states failed");
+    gb_launch(GB_PDL_ELEMENTWISE, lin_pieces_plan_kernel, dim3(1), dim3(32), 0, stream, seq_first_row, seq_start_pos, S, P, piece_len, meta);
+    int rc = gb_check_launch("gb_decay_linear_pieces (plan)");
+    if (rc) return rc;
+    const int* first = meta, *start = meta + P + 1, *slot = start + P;
+    rc = gb_channel_delta(qkv, ldq, nullptr, 0, nullptr, 0, nullptr, decay, piece_state, (long long)(heads * numbers), out, first, start, slot,
+                          P, heads, heads, dk, dv, P, 1, status, 1, CD_PLAIN | (silu_in ? CD_SILU_INPUTS : 0), stream);
+    if (rc) return rc;
+    gb_launch(GB_PDL_ELEMENTWISE, lin_chain_kernel, dim3(S, heads, gb_ceil_div((long long)numbers, 256)), dim3(256), 0, stream,
+              (const int*)meta, P, seq_first_row, seq_start_pos, seq_slots, decay, piece_state, state, state_stride, S, heads, (int)numbers,
+              num_slots, write_state);
+    rc = gb_check_launch("gb_decay_linear_pieces (chain)");
+    if (rc) return rc;
+    gb_launch(GB_PDL_ELEMENTWISE, lin_carry_kernel, dim3(P, heads, gb_ceil_div(dv, LC_COLS)), dim3(256), 0, stream, qkv, ldq,
+              (const int*)meta, P, seq_first_row, decay, (const float*)piece_state, out, heads, dk, dv, piece_len, silu_in);
+    return gb_check_launch("gb_decay_linear_pieces (carry)");
+}
+
+// ----------------------------------------------------------------------------------------------
 // The same recurrence for steps in which every request brings ONE token (decoding): the work is reading and writing
 // S once, so the layout is chosen for that. One block per (request, head), eight warps; warp w owns rows
 // 16 w .. 16 w + 15 of S and lane l the columns l, l + 32, l + 64, l + 96: every load and store of a warp is a row

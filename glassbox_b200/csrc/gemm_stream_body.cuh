@@ -465,7 +465,7 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             const float g = fminf(v[0] + bg, a.unit_limit);
             const float u = fminf(fmaxf(v[1] + bu, -a.unit_limit), a.unit_limit);
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] =
-                a.unit_slope < 0.f ? __float2bfloat16_rn(gb_gelu_tanh(v[0] + bg) * (v[1] + bu))      // the GELU unit, nothing clamped
+                a.unit_slope < 0.f ? __float2bfloat16_rn(gb_gelu_tanh_fast(v[0] + bg) * (v[1] + bu))      // the GELU unit, nothing clamped
                                    : __float2bfloat16_rn(g / (1.0f + __expf(-a.unit_slope * g)) * (u + 1.0f));
         } else if (a.mode == WS_STORE_BF16) {
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(v[0]);

@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                             for (int e = 0; e < 4; ++e) {
                                 const int j = j4 + e;
                                 if (unit.slope < 0.f) {      // the GELU unit: gelu_tanh(G) * U, nothing clamped
-                                    r[j] = __float_as_uint(gb_gelu_tanh(__uint_as_float(r[j]) + bg[e]) * (__uint_as_float(u[j]) * inv_rms + bu[e]));
+                                    r[j] = __float_as_uint(gb_gelu_tanh_fast(__uint_as_float(r[j]) + bg[e]) * (__uint_as_float(u[j]) * inv_rms + bu[e]));
                                     continue;
                                 }
                                 const float g = fminf(__uint_as_float(r[j]) + bg[e], unit.limit);

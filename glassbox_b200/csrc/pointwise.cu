@@ -278,10 +278,48 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     }
 }
 
+// The same for long rows (a norm that spans all heads): one block per (row, head), the sum of squares meets in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_head_norm_wide_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                                                   long long ldg, const float* __restrict__ w, T* __restrict__ out,
+                                                                   int n, int heads, int v, float eps, int gate_silu) {
+    __shared__ float partial[8];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row = blockIdx.x / heads, head = blockIdx.x % heads;
+    const float* src = o + ((size_t)row * heads + head) * v;
+    const float* g = gate + (size_t)row * ldg + (size_t)head * v;
+    T* dst = out + ((size_t)row * heads + head) * v;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < v; j += 256) ss = fmaf(src[j], src[j], ss);
+    ss = gb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += partial[i];
+    const float s = 1.0f / sqrtf(ss / (float)v + eps);
+    for (int j = threadIdx.x; j < v; j += 256) {
+        const float sig = 1.0f / (1.0f + expf(-g[j]));
+        dst[j] = gb_from_float<T>(src[j] * s * w[j] * (gate_silu ? g[j] * sig : sig));
+    }
+}
+
 GB_EXPORT int gb_gated_head_norm(const float* o, const float* gate, long long ldg, const float* w, void* out, int out_dtype,
                                  int n, int heads, int v, float eps, int gate_silu, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && heads > 0 && v > 0, "gb_gated_head_norm: bad sizes");
     if (n == 0) return 0;
+    if (v > 256) {
+        if (out_dtype == GB_F32)
+            gb_launch(GB_PDL_ELEMENTWISE, gated_head_norm_wide_kernel<float>, dim3(n * heads), dim3(256), 0, stream, o, gate, ldg, w,
+                      (float*)out, n, heads, v, eps, gate_silu);
+        else if (out_dtype == GB_BF16)
+            gb_launch(GB_PDL_ELEMENTWISE, gated_head_norm_wide_kernel<__nv_bfloat16>, dim3(n * heads), dim3(256), 0, stream, o, gate, ldg, w,
+                      (__nv_bfloat16*)out, n, heads, v, eps, gate_silu);
+        else
+            GB_REQUIRE(false, "gb_gated_head_norm: unsupported output dtype %d", out_dtype);
+        return gb_check_launch("gb_gated_head_norm");
+    }
     const int blocks = gb_ceil_div((long long)n * heads, 4);
     if (out_dtype == GB_F32)
         gb_launch(GB_PDL_ELEMENTWISE, gated_head_norm_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, (float*)out, n,

@@ -116,6 +116,7 @@ _SIGNATURES = {
     "gb_channel_delta_decode_supported": [_I, _I],
     "gb_channel_delta_decode": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _LL, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                 _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+    "gb_decay_linear_pieces": [_P, _LL, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P],
     "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "gb_streams_broadcast": [_P, _P, _I, _I, _I, _P],
     "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _I, _P, _LL, _P, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
@@ -1185,6 +1186,36 @@ def decay_linear_attention(qkv: torch.Tensor, decay: torch.Tensor, state: torch.
     _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), 0, 0, 0, 0, 0, _ptr(decay), _ptr(state), state.stride(0), _ptr(out),
           _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, heads, dk, dv, state.shape[0],
           1 if write_state else 0, _ptr(status), 1, CD_PLAIN | (CD_SILU_INPUTS if silu_inputs else 0), _stream())
+
+
+#: rows of a piece when a long portion of linear attention with a fixed decay is cut up, and from how many rows on it is
+LINEAR_PIECE_ROWS, LINEAR_PIECES_FROM = 128, 384
+
+
+def linear_pieces_needed(n: int, num_seqs: int) -> int:
+    """How many pieces ``decay_linear_attention_pieces`` may need for a step of ``n`` rows in ``num_seqs`` sequences."""
+    return n // LINEAR_PIECE_ROWS + num_seqs
+
+
+def decay_linear_attention_pieces(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,
+                                  seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int, dk: int, dv: int, write_state: bool,
+                                  status: torch.Tensor, meta: torch.Tensor, piece_state: torch.Tensor, silu_inputs: bool = True) -> None:
+    """``decay_linear_attention`` with every request's rows cut into pieces of ``LINEAR_PIECE_ROWS`` that walk side by side from a
+    zero state; the pieces' states are then chained and q^T S_start is added to every read-out. The same sums in another
+    order: the chain of dependent updates is one piece long. ``meta`` int32 [4 * P + 2 * num_seqs + 1] and ``piece_state`` float32
+    [P, heads * dk * dv] are scratch, P = ``linear_pieces_needed``."""
+    _cuda(qkv, decay, state, out, seq_first_row, seq_start_pos, seq_slots, status, meta, piece_state)
+    n, S = qkv.shape[0], seq_start_pos.shape[0]
+    P = piece_state.shape[0]
+    for t in (qkv, decay, state, out, piece_state):
+        assert t.dtype == torch.float32
+    assert qkv.shape[1] == 2 * heads * dk + heads * dv and qkv.stride(1) == 1 and out.shape == (n, heads * dv) and out.is_contiguous()
+    assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and decay.numel() == heads
+    assert P >= linear_pieces_needed(n, S) and piece_state.shape[1] == heads * dk * dv and piece_state.is_contiguous()
+    assert meta.dtype == torch.int32 and meta.numel() >= 4 * P + 2 * S + 1 and meta.is_contiguous()
+    _call("gb_decay_linear_pieces", _ptr(qkv), qkv.stride(0), _ptr(decay), _ptr(state), state.stride(0), _ptr(out), _ptr(seq_first_row),
+          _ptr(seq_start_pos), _ptr(seq_slots), S, n, heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status),
+          1 if silu_inputs else 0, LINEAR_PIECE_ROWS, P, _ptr(meta), _ptr(piece_state), _stream())
 
 
 def decay_linear_attention_decode(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,

@@ -60,11 +60,19 @@ class DecayLinearAttention(Mixer):
         proj = ctx.scratch("lin_proj", (n, ld), f32)[:, :self.in_cols]
         linear(ctx, h, self.params["w_in"], proj)
         o = ctx.scratch("lin_o", (n, self.v_cols), f32)
-        # single tokens: the form that reads and writes S once, in whole rows; portions: the walk over tokens
-        run = (kernels.decay_linear_attention_decode if ctx.decode_only and kernels.channel_delta_decode_supported(self.dk, self.dv)
-               else kernels.decay_linear_attention)
-        run(proj[:, :self.gate_at], self._decay, cache.state, o, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, self.H, self.dk,
-            self.dv, writes_cache, ctx.status, silu_inputs=True)
+        args = (proj[:, :self.gate_at], self._decay, cache.state, o, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, self.H, self.dk,
+                self.dv, writes_cache, ctx.status)
+        if ctx.decode_only and kernels.channel_delta_decode_supported(self.dk, self.dv):
+            # single tokens: the form that reads and writes S once, in whole rows
+            kernels.decay_linear_attention_decode(*args, silu_inputs=True)
+        elif ctx.max_rows_per_seq >= kernels.LINEAR_PIECES_FROM:
+            # a long portion: its pieces walk side by side, their states are chained afterwards (the decay is a constant)
+            pieces = kernels.linear_pieces_needed(n, ctx.seq_start_pos.shape[0])
+            meta = ctx.scratch("lin_piece_meta", (1, 4 * pieces + 2 * ctx.seq_start_pos.shape[0] + 1), torch.int32, grow=True)
+            piece_state = ctx.scratch("lin_piece_state", (pieces, self.H * self.dk * self.dv), f32, grow=True)
+            kernels.decay_linear_attention_pieces(*args, meta.view(-1), piece_state, silu_inputs=True)
+        else:
+            kernels.decay_linear_attention(*args, silu_inputs=True)
         att = ctx.scratch("att", (n, self.v_cols))
         # the norm runs over the concatenated heads: one "head" of heads * value_dim channels
         kernels.gated_head_norm(o, proj[:, self.gate_at:], self.params["out_norm"], att, 1, self.spec.norm_eps)

@@ -227,7 +227,7 @@ def _identity_rows(pieces):
     return out
 
 
-@pytest.mark.parametrize("H, D, V", [(3, 10, 6), (4, 64, 64), (1, 8, 1), (2, 128, 64), (2, 7, 33), (2, 200, 16)])
+@pytest.mark.parametrize("H, D, V", [(3, 10, 6), (4, 64, 64), (1, 8, 1), (2, 128, 64), (2, 7, 33), (2, 200, 16), (5, 32, 128)])
 def test_lightning_recurrence_norm_and_gate(H, D, V):
     """The recurrence with a fixed decay per head (one, zero and between), SiLU on its inputs, the joint norm and the gate,
     for requests in portions and single tokens with the state carried in slots."""
@@ -261,6 +261,52 @@ def test_lightning_recurrence_norm_and_gate(H, D, V):
     for r in range(len(lengths)):
         want = plain.lightning(rows_in[r], W, "", m, 1e-5)
         np.testing.assert_allclose(got[r], want, atol=3e-5 * max(1.0, np.abs(want).max()), rtol=1e-4, err_msg=f"request {r}")
+
+
+@pytest.mark.parametrize("H, D, V", [(3, 10, 6), (4, 64, 64), (2, 128, 128), (2, 40, 70), (1, 200, 16)])
+def test_lightning_over_long_portions_in_pieces(H, D, V):
+    """Long portions cut into pieces that walk side by side and are chained afterwards equal the walk over the whole portion:
+    requests of unequal length side by side, a padding sequence between them, portions that end inside a piece, a state carried
+    in from an earlier step and out to a later one, decays of one, zero and between."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(H * 100 + D)
+    decay = ([1.0, 0.0, 0.5, 0.97, 0.999] * 2)[:H]
+    m = {"heads": H, "dim": D, "vdim": V, "decay": decay}
+    W = _identity_rows([("q", H * D), ("k", H * D), ("v", H * V), ("g", H * V)])
+    W.update({"o": np.eye(H * V), "norm": np.ones(H * V)})
+    cols = 2 * H * D + 2 * H * V
+    lengths = [700, 130, 3, 515]
+    rows_in = [_rounded(rng.standard_normal((n, cols)), torch.float32) for n in lengths]
+    rows_in = [np.concatenate([r[:, :2 * H * D + H * V], np.full((len(r), H * V), 30.0)], 1) for r in rows_in]      # (gate wide open)
+    slots = [2, 0, 3, 5]
+    state = torch.zeros((7, H * D * V), device=DEV)
+    state[[1, 4, 6]] = 3.0
+    steps = [[(0, 5), (3, 129)], [(0, 400), None, (1, 130), (2, 3), (3, 386)], [(0, 295), None]]
+    got, at, status = [np.zeros((n, H * V)) for n in lengths], [0] * len(lengths), _status()
+    for step in steps:
+        n, row_seq, positions, first, start = _step_meta(step, at)
+        proj = _f32(_gather(step, at, rows_in, cols))
+        o = torch.full((n, H * V), float("nan"), device=DEV)
+        seq_slots = _i32([0 if e is None else slots[e[0]] for e in step])
+        pieces = kernels.linear_pieces_needed(n, len(step))
+        meta = torch.zeros(4 * pieces + 2 * len(step) + 1, dtype=torch.int32, device=DEV)
+        piece_state = torch.full((pieces, H * D * V), float("nan"), device=DEV)
+        kernels.decay_linear_attention_pieces(proj[:, :2 * H * D + H * V], _f32(decay), state, o, first, start, seq_slots, H, D, V, True,
+                                              status, meta, piece_state)
+        _scatter(step, at, o.cpu().numpy(), got)
+    assert int(status.item()) == 0 and bool((state[[1, 4, 6]] == 3.0).all())
+    for r in range(len(lengths)):
+        q = plain.silu(rows_in[r][:, :H * D]).reshape(-1, H, D)
+        k = plain.silu(rows_in[r][:, H * D:2 * H * D]).reshape(-1, H, D)
+        v = plain.silu(rows_in[r][:, 2 * H * D:2 * H * D + H * V]).reshape(-1, H, V)
+        want = np.zeros((lengths[r], H, V))
+        for h in range(H):
+            S = np.zeros((D, V))
+            for t in range(lengths[r]):
+                S = decay[h] * S + np.outer(k[t, h], v[t, h])
+                want[t, h] = S.T @ q[t, h]
+        np.testing.assert_allclose(got[r], want.reshape(lengths[r], -1), atol=1e-4 * max(1.0, np.abs(want).max()), rtol=2e-4,
+                                   err_msg=f"request {r}")
 
 
 def test_lightning_in_closed_form():
