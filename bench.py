@@ -560,16 +560,16 @@ def babotar_raw(size: dict, own: dict, max_positions: int = 8192) -> dict:
         mlp = {"kind": "dense", "ff": size["ff"]}
         if i % 2:
             lf = dict(own["left"])
-            lf.update(scale=lf["dim"] ** -0.5, softcap=50.0,
-                      rot={"base": 10000.0, "dims": lf["dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
-            layers.append({"type": "parallel", "mixer": {"left": lf, "right": dict(own["right"]), "left_scale": 0.6, "right_scale": 0.9},
+            lf.update(scale=lf["dim"] ** -0.5, softcap=30.0,
+                      rot={"base": 10000.0, "dims": lf["dim"], "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}})
+            layers.append({"type": "parallel", "mixer": {"left": lf, "right": dict(own["right"]), "left_scale": 0.8, "right_scale": 1.1},
                            "mlp": mlp})
         else:
             m = dict(own["lightning"])
             m["decay"] = [1.0 - 2.0 ** -(3 + 5 * h / max(m["heads"] - 1, 1)) for h in range(m["heads"])]
             layers.append({"type": "lightning", "mixer": m, "mlp": mlp})
     return make_babotar_raw_config(vocab=size["vocab"], width=size["width"], max_positions=max_positions, layers=layers, streams=4,
-                                   residual_mult=0.7, canon_taps=4)
+                                   residual_mult=0.5, canon_taps=4)
 
 
 def babotar_workload(args):

@@ -580,7 +580,7 @@ def bench_babotar() -> None:
         o = torch.empty_like(q)
         wide = torch.empty(t_len, H * G * hd, device=DEV)
         talk = torch.eye(H, device=DEV) + 0.1 * torch.randn(H, H, device=DEV)
-        own = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, value_heads=G, page_size=ps, scale=hd ** -0.5, softcap=50.0, unit_sink=True,
+        own = dict(heads=H, kv_heads=G, dim=hd, vdim=hd, value_heads=G, page_size=ps, scale=hd ** -0.5, softcap=30.0, unit_sink=True,
                    window=None, status=status)
         seen = t_len * (t_len + 1) // 2
         fl_own, fl_like = 2.0 * seen * H * (hd + G * hd), 2.0 * seen * H * (hd + hd)

@@ -95,9 +95,9 @@ CONFIGS = {
     ], streams=1, mult=1.0, taps=1),
     # sizes that fit no vector width: odd row lengths everywhere, so every kernel's aligned fast path must step aside
     "ragged": lambda: config(67, 50, [
-        parallel(left(3, 1, 10, 7, rot(6, 77.0, (3.0, 32, 4.0, 1.0)), softcap=4.0), right(3, 1, 9, 7, 3), 0.6, 0.9, dense(11)),
+        parallel(left(3, 1, 10, 7, rot(6, 77.0, (3.0, 32, 4.0, 1.0)), softcap=4.0), right(3, 1, 9, 7, 3), 0.75, 1.2, dense(11)),
         lightning(3, 7, 5, (0.9, 0.8, 0.7), dense(9)),
-    ], streams=3, mult=0.7, taps=3),
+    ], streams=5, mult=0.9, taps=5),
 }
 
 
