@@ -256,14 +256,16 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     const T* __restrict__ q, float* __restrict__ out, float* __restrict__ ml, const T* __restrict__ kcache, const T* __restrict__ vcache,
     const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
     int n, int H, int G, int D, int V, int VG, int page_size, long long num_pages, float scale, float cap, float unit, int window,
-    int shares, int* __restrict__ status) {
+    int shares, int col_blocks, int* __restrict__ status) {
     constexpr int KB = (NC > 8 && !VEC) ? 4 : 8;       // value rows in flight together
     __shared__ float qs[R * SA_MAX_DIM];
     __shared__ float part[TKD_WARPS][R][NC * 32 + 2];
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x, head0 = blockIdx.y * R, share = blockIdx.z;
+    // a wide value row of more than 256 channels is cut into column blocks of 256 (each forms the scores again: a key row is
+    // an eighth of a value row's bytes), so that R heads' sums of a block's columns fit a thread's registers
+    const int row = blockIdx.x, head0 = blockIdx.y * R, share = blockIdx.z / col_blocks, cb = blockIdx.z % col_blocks;
     if (row >= n) return;
     const int g = head0 / (H / G);
     const int pos = positions[row];
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     // this block's share of the visible keys: whole chunks of 32, the same count for every share but the last
     const int chunks = (pos - first) / 32 + 1, per_share = (chunks + shares - 1) / shares;
     const int c_lo = share * per_share, c_hi = min(chunks, c_lo + per_share);
-    const int wide = VG * V;
+    const int wide = VG * V, bw = wide / col_blocks, col0 = cb * bw;
     float m[R], l[R], acc[R][NC];
     int voff[NC];
 #pragma unroll
@@ -292,9 +294,9 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     }
 #pragma unroll
     for (int j = 0; j < NC; ++j) {
-        const int i = VEC ? lane * NC + j : lane + 32 * j;
+        const int il = VEC ? lane * NC + j : lane + 32 * j, i = col0 + il;
         const int c = VG == 1 ? g : i / V;
-        voff[j] = i < wide ? c * page_size * V + i % V : 0;          // (lanes past the row read a channel they never store)
+        voff[j] = il < bw ? c * page_size * V + i % V : 0;           // (lanes past the block's columns read a channel they never store)
     }
     for (int chunk = c_lo + warp; chunk < c_hi; chunk += TKD_WARPS) {
         const int base = first + chunk * 32, key = base + lane;
@@ -381,8 +383,8 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
     }
     __syncthreads();
     const bool final_ = shares == 1;
-    for (int idx = threadIdx.x; idx < R * wide; idx += TKD_WARPS * 32) {
-        const int r = idx / wide, i = idx % wide;
+    for (int idx = threadIdx.x; idx < R * bw; idx += TKD_WARPS * 32) {
+        const int r = idx / bw, i = idx % bw;
         float top = (final_ && unit > 0.f) ? 0.f : -INFINITY;
 #pragma unroll
         for (int w = 0; w < TKD_WARPS; ++w) top = fmaxf(top, part[w][r][NC * 32]);
@@ -398,10 +400,10 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
         }
         const size_t at = ((size_t)share * n + row) * H + head0 + r;
         if (final_) {
-            out[at * wide + i] = den > 0.f ? sum / den : 0.f;
+            out[at * wide + col0 + i] = den > 0.f ? sum / den : 0.f;
         } else {
-            out[at * wide + i] = sum;
-            if (i == 0) {
+            out[at * wide + col0 + i] = sum;
+            if (i == 0 && cb == 0) {
                 ml[at * 2] = top;
                 ml[at * 2 + 1] = den;
             }
@@ -410,14 +412,17 @@ __global__ void __launch_bounds__(TKD_WARPS * 32) talking_attention_decode_kerne
 }
 
 GB_EXPORT int gb_talking_attention_decode_plan(int H, int G, int V, int VG) {
-    // heads per block: the largest of 8, 4, 2, 1 that divides the group and keeps R * NC within 32; 0: no kernel
+    // column blocks * 10000 + heads per block * 100 + pieces: a wide row that is a multiple of 256 channels goes in column blocks
+    // of 256; heads per block: the largest of 8, 4, 2, 1 that divides the group and keeps R * NC within 32; 0: no kernel
     const int wide = VG * V;
+    const int col_blocks = (wide > 256 && wide % 256 == 0) ? wide / 256 : 1;
+    const int bw = wide / col_blocks;
     int nc = 1;
-    while (nc < 8 && nc * 32 < wide) nc *= 2;
-    if (nc * 32 < wide) nc = wide <= 384 ? 12 : 16;
-    if (nc * 32 < wide) return 0;
+    while (nc < 8 && nc * 32 < bw) nc *= 2;
+    if (nc * 32 < bw) nc = bw <= 384 ? 12 : 16;
+    if (nc * 32 < bw) return 0;
     for (int r = 8; r >= 1; r /= 2)
-        if ((H / G) % r == 0 && r * nc <= 32) return r * 100 + nc;
+        if ((H / G) % r == 0 && r * nc <= 32) return col_blocks * 10000 + r * 100 + nc;
     return 0;
 }
 
@@ -431,14 +436,14 @@ GB_EXPORT int gb_talking_attention_decode(const void* q, float* out, float* ml, 
     GB_REQUIRE(plan > 0, "gb_talking_attention_decode: %d value heads of %d channels are not built", VG, V);
     GB_REQUIRE(shares >= 1 && shares <= 64 && (shares == 1 || ml != nullptr), "gb_talking_attention_decode: %d shares", shares);
     if (n == 0) return 0;
-    const int R = plan / 100, nc = plan % 100;
-    const dim3 grid(n, H / R, shares);
+    const int col_blocks = plan / 10000, R = plan % 10000 / 100, nc = plan % 100;
+    const dim3 grid(n, H / R, shares * col_blocks);
     // (the vector form: bfloat16, a wide row of exactly 32 * nc channels, a lane's nc channels inside one value head)
-    const bool vec = dtype == GB_BF16 && VG * V == 32 * nc && nc % 2 == 0 && V % nc == 0;
+    const bool vec = dtype == GB_BF16 && VG * V == 32 * nc * col_blocks && nc % 2 == 0 && V % nc == 0;
 #define TKD_LAUNCH(T, RR, N, VV)                                                                                                        \
     gb_launch(GB_PDL_ATTENTION, talking_attention_decode_kernel<T, RR, N, VV>, grid, dim3(TKD_WARPS * 32), 0, stream, (const T*)q, out, \
               ml, (const T*)kcache, (const T*)vcache, block_tables, max_pages, row_seq, positions, n, H, G, D, V, VG, page_size,        \
-              num_pages, scale, cap, unit, window, shares, status)
+              num_pages, scale, cap, unit, window, shares, col_blocks, status)
 #define TKD_CASE(T, RR, N)                                                                                                             \
     if (R == RR && nc == N) {                                                                                                          \
         if (sizeof(T) == 2 && N % 2 == 0 && vec) TKD_LAUNCH(T, RR, (N % 2 == 0 ? N : 2), (sizeof(T) == 2));                            \

@@ -1713,7 +1713,7 @@ def talking_decode_shares(n: int, heads: int, kv_heads: int, vdim: int, value_he
     """Into how many shares the decoding kernel cuts a row's keys: enough blocks for two per multiprocessor, no share shorter
     than 256 keys, at most 16."""
     plan = lib().gb_talking_attention_decode_plan(heads, kv_heads, vdim, value_heads)
-    blocks = max(1, n * (heads // max(plan // 100, 1)))
+    blocks = max(1, n * (heads // max(plan % 10000 // 100, 1)) * max(plan // 10000, 1))
     return int(max(1, min(16, -(-296 // blocks), max(1, reach // 256), 4096 // heads)))
 
 

@@ -452,7 +452,8 @@ def _left_by_identity(H, G, D, V, rng, rotation, softcap, scale):
 @pytest.mark.parametrize("H, G, D, V, rot_dims, scaling, cap", [
     (6, 2, 20, 12, 12, (4.0, 64, 8.0, 2.0), 5.0), (4, 4, 16, 24, 16, None, 2.0), (8, 2, 64, 64, 64, (8.0, 128, 16.0, 1.0), 30.0),
     (4, 1, 128, 64, 128, None, None), (1, 1, 8, 1, 2, (2.0, 8, 2.0, 1.0), None), (3, 1, 10, 7, 6, (3.0, 32, 4.0, 1.0), 4.0),
-    (4, 4, 32, 32, 0, None, 10.0), (16, 4, 64, 64, 32, None, 50.0), (2, 2, 128, 128, 64, None, None)])
+    (4, 4, 32, 32, 0, None, 10.0), (16, 4, 64, 64, 32, None, 50.0), (2, 2, 128, 128, 64, None, None), (8, 4, 32, 128, 16, None, 6.0),
+    (6, 6, 16, 128, 0, None, None)])
 def test_talking_attention_kernels(how, dtype, H, G, D, V, rot_dims, scaling, cap):
     """Three requests of unequal length whose pages lie interleaved, brought in by portions and single tokens, against the
     plain mixer over each whole request."""
