@@ -736,3 +736,45 @@ def test_greedy_generation_through_the_entry_point(dtype, tmp_path_factory):
                 break                                                # rounding chose the runner-up: the texts part ways
             assert tok == best, f"{dtype} prompt of {len(p)}: token {i} is {tok}, plain says {best}"
             seq.append(tok)
+
+
+def test_a_trace_replayed_from_the_command_line(tmp_path_factory, tmp_path):
+    """``bin/trace_run`` as a user runs it: steps on standard input, logits in files; four live requests at most in a pool that
+    holds only what is live, portions beside single tokens, requests that end and others that take their slots and pages."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from replay_util import TRACE_RUN, live_tokens_needed
+    model = _model("odd", tmp_path_factory)
+    cfg, _, folder, _ = model
+    reqs = {"a": _tokens(cfg, 150, 61), "b": _tokens(cfg, 40, 62), "c": _tokens(cfg, 66, 63), "d": _tokens(cfg, 9, 64), "e": _tokens(cfg, 70, 65)}
+    plan = [[("a", 64), ("b", 2)], [("a", 3), ("b", 1), ("c", 29)], [("a", 1), ("b", 16), ("c", 1), ("d", 2)],
+            [("a", 16), ("b", 21), ("c", 36), ("d", 7)], [("a", 1), ("e", 64)], [("a", 64), ("e", 2)], [("a", 1), ("e", 4)]]
+    at, steps = {k: 0 for k in reqs}, []
+    for i, step in enumerate(plan):
+        entries, end = [], []
+        for rid, k in step:
+            entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + k], "want": list(range(k))})
+            at[rid] += k
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+        steps.append({"step": i, "entries": entries, "end": end})
+    assert at == {k: len(v) for k, v in reqs.items()}
+    out = str(tmp_path / "out")
+    os.makedirs(out)
+    proc = subprocess.run([sys.executable, TRACE_RUN, "--model", folder, "--dtype", "float32", "--out", out, "--max-tokens",
+                           str(live_tokens_needed(steps))], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(plan))]
+    got = {k: [] for k in reqs}
+    for i, step in enumerate(plan):
+        rows = np.fromfile(os.path.join(out, f"{i}.f32"), dtype="<f4").reshape(-1, cfg["vocab"])
+        row = 0
+        for rid, k in step:
+            got[rid].append(rows[row:row + k])
+            row += k
+        assert row == len(rows)
+    for rid in reqs:
+        assert_logits_close(np.concatenate(got[rid], 0), _want(model, reqs[rid]), "float32", f"replayed request {rid}")
