@@ -752,8 +752,10 @@ __global__ void __launch_bounds__(256) talk_combine_kernel(const float* __restri
         }
         __syncthreads();
     }
-    for (int idx = g_lo * V + threadIdx.x; idx < g_hi * V; idx += 256) {
-        const int g = idx / V, ch = idx % V;
+    // (with few rows the channels of a value head are cut over blockIdx.z, so that the merge has blocks enough)
+    const int cw = (V + gridDim.z - 1) / gridDim.z, ch_lo = blockIdx.z * cw, ch_n = max(0, min(V, ch_lo + cw) - ch_lo);
+    for (int t = threadIdx.x; t < (g_hi - g_lo) * ch_n; t += 256) {
+        const int g = g_lo + t / ch_n, ch = ch_lo + t % ch_n, idx = g * V + ch;
         float v;
         if (shares > 1) {
             float a0 = 0.f, a1 = 0.f;
@@ -770,8 +772,8 @@ __global__ void __launch_bounds__(256) talk_combine_kernel(const float* __restri
         rows[idx] = v;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < per * V; idx += 256) {
-        const int h = c * per + idx / V, ch = idx % V;
+    for (int t = threadIdx.x; t < per * ch_n; t += 256) {
+        const int h = c * per + t / ch_n, ch = ch_lo + t % ch_n;
         float acc;
         if (talk) {
             float a0 = 0.f, a1 = 0.f;
@@ -795,8 +797,9 @@ static int tkc_launch(const float* o, const float* ml, const float* talk, void* 
     const size_t smem = ((size_t)H * V + (size_t)H * shares) * sizeof(float);
     GB_REQUIRE(smem <= 200 * 1024, "gb_talk_combine: %d heads of %d channels in %d shares do not fit a block's shared memory", H, V, shares);
     if (smem > 48 * 1024) cudaFuncSetAttribute(talk_combine_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gb_launch(GB_PDL_ELEMENTWISE, talk_combine_kernel<T>, dim3(n, G), dim3(256), smem, stream, o, ml, talk, (T*)att, positions, n, H, G, V,
-              VG, shares, unit);
+    const int cuts = (long long)n * G >= 296 ? 1 : (int)min((long long)gb_ceil_div(V, 16), (long long)gb_ceil_div(296, (long long)n * G));
+    gb_launch(GB_PDL_ELEMENTWISE, talk_combine_kernel<T>, dim3(n, G, cuts), dim3(256), smem, stream, o, ml, talk, (T*)att, positions, n, H, G,
+              V, VG, shares, unit);
     return gb_check_launch("gb_talk_combine");
 }
 
