@@ -838,7 +838,8 @@ __global__ void __launch_bounds__(256) residual_conv_kernel(const T* __restrict_
                                                             const float* __restrict__ state, long long state_stride, long long state_off,
                                                             const int* __restrict__ row_seq, const int* __restrict__ positions,
                                                             const int* __restrict__ seq_first_row, const int* __restrict__ seq_slots,
-                                                            int n, int C, int taps, int num_slots, int* __restrict__ status) {
+                                                            int n, int C, int taps, int num_slots, int shift_here,
+                                                            int* __restrict__ status) {
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int row = blockIdx.x;
@@ -852,14 +853,20 @@ __global__ void __launch_bounds__(256) residual_conv_kernel(const T* __restrict_
         atomicOr(status, GB_STATUS_BAD_SLOT);
         return;
     }
-    const float* st = state + (size_t)slot * state_stride + state_off;
+    float* st = const_cast<float*>(state) + (size_t)slot * state_stride + state_off;
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {
         const int src = row - (taps - 1) + j;
         const float v = src >= r0 ? gb_to_float(x[(size_t)src * C + ch]) : st[(size_t)(taps - 1 - (r0 - src)) * C + ch];
         acc = fmaf(gb_to_float(w[(size_t)ch * taps + j]), v, acc);
     }
-    y[(size_t)row * C + ch] = gb_from_float<T>(gb_to_float(x[(size_t)row * C + ch]) + acc);
+    const float own = gb_to_float(x[(size_t)row * C + ch]);
+    y[(size_t)row * C + ch] = gb_from_float<T>(own + acc);
+    if (shift_here) {
+        // every request brings one row: this thread is the only reader of its channel's last inputs, so it moves them up itself
+        for (int i = 0; i + 2 < taps; ++i) st[(size_t)i * C + ch] = st[(size_t)(i + 1) * C + ch];
+        if (taps > 1) st[(size_t)(taps - 2) * C + ch] = own;
+    }
 }
 
 template <typename T>
@@ -889,11 +896,13 @@ static int residual_conv_launch(const void* x, const void* w, void* y, float* st
                                 const int* row_seq, const int* positions, const int* seq_first_row, const int* seq_start_pos,
                                 const int* seq_slots, int n, int S, int C, int taps, int num_slots, int update_state, int* status,
                                 cudaStream_t stream) {
+    // update_state 2: every request brings exactly one row, and the kernel that reads the last inputs also moves them up
     dim3 grid(n, gb_ceil_div(C, 256));
     gb_launch(GB_PDL_ELEMENTWISE, residual_conv_kernel<T, TW>, grid, dim3(256), 0, stream, (const T*)x, (const TW*)w, (T*)y,
-              (const float*)state, state_stride, state_off, row_seq, positions, seq_first_row, seq_slots, n, C, taps, num_slots, status);
+              (const float*)state, state_stride, state_off, row_seq, positions, seq_first_row, seq_slots, n, C, taps, num_slots,
+              update_state == 2 ? 1 : 0, status);
     int rc = gb_check_launch("gb_residual_conv");
-    if (rc || !update_state || taps == 1) return rc;
+    if (rc || update_state != 1 || taps == 1) return rc;
     dim3 grid2(S, gb_ceil_div(C, 256));
     gb_launch(GB_PDL_ELEMENTWISE, residual_conv_state_kernel<T>, grid2, dim3(256), 0, stream, (const T*)x, state, state_stride, state_off,
               seq_first_row, seq_start_pos, seq_slots, S, C, taps, num_slots);

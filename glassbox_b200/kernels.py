@@ -1237,10 +1237,11 @@ def decay_linear_attention_decode(qkv: torch.Tensor, decay: torch.Tensor, state:
 
 def residual_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torch.Tensor, state_off: int, row_seq: torch.Tensor,
                   positions: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor,
-                  update_state: bool, status: torch.Tensor) -> None:
+                  update_state: bool, status: torch.Tensor, single_rows: bool = False) -> None:
     """y[t, c] = x[t, c] + sum_j w[c, j] * x[t - (taps - 1) + j, c] along each request's rows (x, y [n, C] in the activation
     dtype, different buffers; sums in float32). Inputs from before the step come from (and, with ``update_state``, the last
-    taps - 1 inputs go to) the request's slot of ``state`` float32 [slots, numbers], at ``state_off``, laid out [taps - 1, C]."""
+    taps - 1 inputs go to) the request's slot of ``state`` float32 [slots, numbers], at ``state_off``, laid out [taps - 1, C].
+    ``single_rows``: every request brings exactly one row; the last inputs are then moved up by the same launch."""
     _cuda(x, w, y, state, row_seq, positions, seq_first_row, seq_start_pos, seq_slots, status)
     n, C = x.shape
     taps = w.shape[1]
@@ -1249,7 +1250,7 @@ def residual_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torc
     assert state_off + (taps - 1) * C <= state.shape[1]
     _call("gb_residual_conv", _ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(y), _ptr(state), state.stride(0), state_off, _ptr(row_seq),
           _ptr(positions), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), n, seq_start_pos.shape[0], C, taps, state.shape[0],
-          1 if update_state else 0, _ptr(status), _stream())
+          (2 if single_rows else 1) if update_state else 0, _ptr(status), _stream())
 
 
 def channel_delta_decode_supported(dk: int, dv: int) -> bool:

@@ -245,7 +245,7 @@ class InputConvolution(Part):
 
     def forward(self, ctx, h, out, state, writes_cache: bool) -> None:
         kernels.residual_conv(h, self.params["weight"], out, state, 0, ctx.row_seq, ctx.positions, ctx.seq_first_row,
-                              ctx.seq_start_pos, ctx.seq_slots, writes_cache, ctx.status)
+                              ctx.seq_start_pos, ctx.seq_slots, writes_cache, ctx.status, single_rows=ctx.decode_only)
 
 
 class HyperConnectionBlock(Part):

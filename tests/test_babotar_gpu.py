@@ -163,7 +163,8 @@ def test_input_convolution_carries_its_last_inputs(dtype, taps, C):
         x = _f32(_gather(step, at, rows_in, C)).to(dtype)
         y = torch.zeros_like(x)
         seq_slots = _i32([0 if e is None else slots[e[0]] for e in step])
-        kernels.residual_conv(x, _f32(w), y, state, off, row_seq, positions, first, start, seq_slots, True, status)
+        single = all(e is None or e[1] == 1 for e in step)          # (then the same launch moves the last inputs up)
+        kernels.residual_conv(x, _f32(w), y, state, off, row_seq, positions, first, start, seq_slots, True, status, single_rows=single)
         _scatter(step, at, y.float().cpu().numpy(), got)
     assert int(status.item()) == 0
     assert bool((state[[1, 3, 6]] == 7.0).all()) and bool((state[:, :off] == 7.0).all()) and bool((state[:, off + max(taps - 1, 1) * C:] == (
