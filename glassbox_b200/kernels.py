@@ -1188,19 +1188,31 @@ def decay_linear_attention(qkv: torch.Tensor, decay: torch.Tensor, state: torch.
           1 if write_state else 0, _ptr(status), 1, CD_PLAIN | (CD_SILU_INPUTS if silu_inputs else 0), _stream())
 
 
-#: rows of a piece when a long portion of linear attention with a fixed decay is cut up, and from how many rows on it is
+#: fewest rows of a piece when a long portion of linear attention with a fixed decay is cut up, and from how many rows on it is
 LINEAR_PIECE_ROWS, LINEAR_PIECES_FROM = 128, 384
 
 
-def linear_pieces_needed(n: int, num_seqs: int) -> int:
+def linear_piece_rows(longest: int, heads: int, dk: int, dv: int) -> int:
+    """Rows of a piece for a step whose longest portion has ``longest`` rows, or 0 where the portion is too short to cut.
+    Short pieces are as good as long ones: the walking kernel is bound by what a multiprocessor issues as much as by the
+    chain (two of its blocks on one multiprocessor take nearly twice as long), so what the pieces buy is the multiprocessors
+    that one walk leaves idle. Measured alone at 8 heads x 128 x 128, 2,048 rows: one walk 690 us, pieces of 128 rows 396 us,
+    of 512 rows 539 us; at 16 heads (128 blocks a walk) one walk 718-736 us, pieces of 128 rows 838 us, of 1,024 rows 1,075 us;
+    inside a model's prompt step the pieces of 128 are the faster form at both sizes (7.86 against 9.65 ms at 8 heads, 15.0
+    against 15.3 ms at 16)."""
+    return LINEAR_PIECE_ROWS if longest >= LINEAR_PIECES_FROM else 0
+
+
+def linear_pieces_needed(n: int, num_seqs: int, piece_rows: int = LINEAR_PIECE_ROWS) -> int:
     """How many pieces ``decay_linear_attention_pieces`` may need for a step of ``n`` rows in ``num_seqs`` sequences."""
-    return n // LINEAR_PIECE_ROWS + num_seqs
+    return n // piece_rows + num_seqs
 
 
 def decay_linear_attention_pieces(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,
                                   seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int, dk: int, dv: int, write_state: bool,
-                                  status: torch.Tensor, meta: torch.Tensor, piece_state: torch.Tensor, silu_inputs: bool = True) -> None:
-    """``decay_linear_attention`` with every request's rows cut into pieces of ``LINEAR_PIECE_ROWS`` that walk side by side from a
+                                  status: torch.Tensor, meta: torch.Tensor, piece_state: torch.Tensor, silu_inputs: bool = True,
+                                  piece_rows: int = LINEAR_PIECE_ROWS) -> None:
+    """``decay_linear_attention`` with every request's rows cut into pieces of ``piece_rows`` that walk side by side from a
     zero state; the pieces' states are then chained and q^T S_start is added to every read-out. The same sums in another
     order: the chain of dependent updates is one piece long. ``meta`` int32 [4 * P + 2 * num_seqs + 1] and ``piece_state`` float32
     [P, heads * dk * dv] are scratch, P = ``linear_pieces_needed``."""
@@ -1211,11 +1223,11 @@ def decay_linear_attention_pieces(qkv: torch.Tensor, decay: torch.Tensor, state:
         assert t.dtype == torch.float32
     assert qkv.shape[1] == 2 * heads * dk + heads * dv and qkv.stride(1) == 1 and out.shape == (n, heads * dv) and out.is_contiguous()
     assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and decay.numel() == heads
-    assert P >= linear_pieces_needed(n, S) and piece_state.shape[1] == heads * dk * dv and piece_state.is_contiguous()
+    assert P >= linear_pieces_needed(n, S, piece_rows) and piece_state.shape[1] == heads * dk * dv and piece_state.is_contiguous()
     assert meta.dtype == torch.int32 and meta.numel() >= 4 * P + 2 * S + 1 and meta.is_contiguous()
     _call("gb_decay_linear_pieces", _ptr(qkv), qkv.stride(0), _ptr(decay), _ptr(state), state.stride(0), _ptr(out), _ptr(seq_first_row),
           _ptr(seq_start_pos), _ptr(seq_slots), S, n, heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status),
-          1 if silu_inputs else 0, LINEAR_PIECE_ROWS, P, _ptr(meta), _ptr(piece_state), _stream())
+          1 if silu_inputs else 0, int(piece_rows), P, _ptr(meta), _ptr(piece_state), _stream())
 
 
 def decay_linear_attention_decode(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor,

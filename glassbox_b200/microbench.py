@@ -665,8 +665,14 @@ def bench_babotar() -> None:
             else:
                 t2 = graph_time(lambda: kernels.channel_delta(qkv, beta, a, dt, al, states[0], out, first, start, slots, H, H, dk, dv, True,
                                                               status, decay_per_head=True), reps=3)
-                print(f"lightning prompt heads {H} x {dk} x {dv}, {n} tokens: {t:7.1f} us = {t / n:5.3f} us per token; delta rule "
-                      f"(one decay per head): {t2:7.1f} us = {t2 / n:5.3f} us per token", flush=True)
+                piece_rows = kernels.linear_piece_rows(n, H, dk, dv) or kernels.LINEAR_PIECE_ROWS
+                pieces = kernels.linear_pieces_needed(n, S, piece_rows)
+                meta = torch.zeros(4 * pieces + 2 * S + 1, dtype=torch.int32, device=DEV)
+                piece_state = torch.empty(pieces, H * dk * dv, device=DEV)
+                t3 = graph_time(lambda: kernels.decay_linear_attention_pieces(qkv, decay, states[0], out, first, start, slots, H, dk, dv, True,
+                                                                              status, meta, piece_state, piece_rows=piece_rows), reps=3)
+                print(f"lightning prompt heads {H} x {dk} x {dv}, {n} tokens: one walk {t:7.1f} us = {t / n:5.3f} us per token, in pieces of "
+                      f"{piece_rows} {t3:7.1f} us; delta rule (one decay per head): {t2:7.1f} us = {t2 / n:5.3f} us per token", flush=True)
     # the convolution on the mixers' input and the gated GELU unit in the products' epilogues
     for d, ff in ((1024, 4096), (2048, 8192)):
         for n in (2048, 64, 8):

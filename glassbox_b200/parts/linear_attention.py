@@ -65,12 +65,13 @@ class DecayLinearAttention(Mixer):
         if ctx.decode_only and kernels.channel_delta_decode_supported(self.dk, self.dv):
             # single tokens: the form that reads and writes S once, in whole rows
             kernels.decay_linear_attention_decode(*args, silu_inputs=True)
-        elif ctx.max_rows_per_seq >= kernels.LINEAR_PIECES_FROM:
+        elif kernels.linear_piece_rows(ctx.max_rows_per_seq, self.H, self.dk, self.dv):
             # a long portion: its pieces walk side by side, their states are chained afterwards (the decay is a constant)
-            pieces = kernels.linear_pieces_needed(n, ctx.seq_start_pos.shape[0])
+            piece_rows = kernels.linear_piece_rows(ctx.max_rows_per_seq, self.H, self.dk, self.dv)
+            pieces = kernels.linear_pieces_needed(n, ctx.seq_start_pos.shape[0], piece_rows)
             meta = ctx.scratch("lin_piece_meta", (1, 4 * pieces + 2 * ctx.seq_start_pos.shape[0] + 1), torch.int32, grow=True)
             piece_state = ctx.scratch("lin_piece_state", (pieces, self.H * self.dk * self.dv), f32, grow=True)
-            kernels.decay_linear_attention_pieces(*args, meta.view(-1), piece_state, silu_inputs=True)
+            kernels.decay_linear_attention_pieces(*args, meta.view(-1), piece_state, silu_inputs=True, piece_rows=piece_rows)
         else:
             kernels.decay_linear_attention(*args, silu_inputs=True)
         att = ctx.scratch("att", (n, self.v_cols))

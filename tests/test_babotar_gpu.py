@@ -289,11 +289,12 @@ def test_lightning_over_long_portions_in_pieces(H, D, V):
         proj = _f32(_gather(step, at, rows_in, cols))
         o = torch.full((n, H * V), float("nan"), device=DEV)
         seq_slots = _i32([0 if e is None else slots[e[0]] for e in step])
-        pieces = kernels.linear_pieces_needed(n, len(step))
+        piece_rows = [128, 192, 320][n % 3]                           # (another length of the pieces at every step)
+        pieces = kernels.linear_pieces_needed(n, len(step), piece_rows)
         meta = torch.zeros(4 * pieces + 2 * len(step) + 1, dtype=torch.int32, device=DEV)
         piece_state = torch.full((pieces, H * D * V), float("nan"), device=DEV)
         kernels.decay_linear_attention_pieces(proj[:, :2 * H * D + H * V], _f32(decay), state, o, first, start, seq_slots, H, D, V, True,
-                                              status, meta, piece_state)
+                                              status, meta, piece_state, piece_rows=piece_rows)
         _scatter(step, at, o.cpu().numpy(), got)
     assert int(status.item()) == 0 and bool((state[[1, 4, 6]] == 3.0).all())
     for r in range(len(lengths)):
